@@ -10,7 +10,7 @@ storage itself.
 
 Caches (one per schedule entry that writes) with the same needs - same heads, head
 size and window - form a group.  A group has its own pool
-[caches_in_group, pages, 2 (K, V), kv_heads, page_size, head_dim], its own page
+[caches_in_group, pages, planes (K, V; or one latent), kv_heads, page_size, head_dim], its own page
 allocator and its own block table [max_seqs, max_blocks] on the device, indexed by
 the request's slot: one page id serves every cache of the group.  A request's
 pages are given back when it ends, and, in a group with a window, as soon as
@@ -36,7 +36,7 @@ class OutOfSlots(RuntimeError):
 @dataclass
 class CacheView:
     """What a mixer sees of the cache during one step."""
-    kv: Optional[torch.Tensor]              # [pages, 2, kv_heads, page_size, head_dim] or None
+    kv: Optional[torch.Tensor]              # [pages, planes, kv_heads, page_size, head_dim] or None
     block_table: Optional[torch.Tensor]     # int32 [max_seqs, max_blocks], rows indexed by request slot
     page_size: int
     state: Optional[torch.Tensor]           # [max_seqs, *state shape] or None
@@ -63,7 +63,7 @@ class _Group:
         self.spec = spec
         self.cache_ids = cache_ids
         self.alloc = PageAllocator(num_pages)
-        self.pool = torch.zeros((len(cache_ids), num_pages, 2, spec.num_kv_heads, page_size, spec.head_dim),
+        self.pool = torch.zeros((len(cache_ids), num_pages, spec.planes, spec.num_kv_heads, page_size, spec.head_dim),
                                 dtype=dtype, device=device)
         self.table = torch.zeros((max_seqs, max_blocks), dtype=torch.int32, device=device)
         self.updates: List[Tuple[int, int]] = []                 # (flat index into table, page)

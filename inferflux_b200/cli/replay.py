@@ -32,7 +32,7 @@ def add_arguments(ap):
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-seqs", type=int, default=8, help="request slots")
+    ap.add_argument("--max-seqs", type=int, default=4, help="request slots (no more requests are live at any time)")
 
 
 def run(args) -> int:

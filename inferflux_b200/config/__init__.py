@@ -3,7 +3,8 @@ from .plan import LayerSpec, ModelPlan, PartSpec, ScheduleEntry, SubPart, defaul
 from .registry import (ConfigError, config_from_dict, load_config, register_architecture,
                        registered_architectures, resolve_architecture)
 from .qwen2 import Qwen2Config
+from .dafolorn import DafolornConfig
 
 __all__ = ["LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "SubPart", "default_schedule", "prenorm_layer", "ConfigError",
            "config_from_dict", "load_config", "register_architecture", "registered_architectures",
-           "resolve_architecture", "Qwen2Config"]
+           "resolve_architecture", "Qwen2Config", "DafolornConfig"]

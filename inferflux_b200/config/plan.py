@@ -73,10 +73,13 @@ class ScheduleEntry:
     """One run of a layer.  `cache` names the cache (and state) index the mixer
     works on; two entries may name the same layer (weights run twice, each with a
     cache of its own) or the same cache (the later entry reads what the earlier one
-    wrote and, with writes_cache False, stores nothing itself)."""
+    wrote and, with writes_cache False, stores nothing itself).  `repeat` counts the runs
+    of a stretch of layers that is gone through several times, for parts that do
+    something different in every run."""
     layer: int
     cache: int
     writes_cache: bool = True
+    repeat: int = 0             # which run of a looped stretch this is (0 for layers that run once)
 
 
 @dataclass
@@ -93,6 +96,7 @@ class ModelPlan:
     final_norm_prefix: str = "model.norm."
     embedding_prefix: str = "model.embed_tokens."
     lm_head_prefix: str = "lm_head."
+    keeps_embedding_output: bool = False      # some block reads the embedding output again (ctx.embedding_output)
 
     @property
     def num_caches(self) -> int:

@@ -39,10 +39,12 @@ def resolve_architecture(raw: dict) -> type:
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         names.append(str(archs[0]))
+    if raw.get("architecture"):                       # some exports name it in the singular
+        names.append(str(raw["architecture"]))
     if raw.get("model_type"):
         names.append(str(raw["model_type"]))
     if not names:
-        raise ConfigError("config.json has neither `architectures` nor `model_type`")
+        raise ConfigError("config.json has neither `architectures`, `architecture` nor `model_type`")
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

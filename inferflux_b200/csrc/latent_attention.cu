@@ -1,0 +1,240 @@
+// Attention whose keys and values of all heads are made from one normed latent
+// vector per token; only the latent is cached (one plane of one "head" of size
+// rank per page slot).
+//
+//   c_j          = rmsnorm(dkv_j) * w_norm                         (latent_norm_append)
+//   k_j,h = Wuk_h c_j ,  v_j,h = Wuv_h c_j
+//   s_ij,h       = scale * q_i,h . k_j,h = scale * (Wuk_h^T q_i,h) . c_j
+//   p_ij,h       = exp(s_ij,h) / (sum_j' exp(s_ij',h) + exp(sink_h))      over the window
+//   o_i,h        = sum_j p_ij,h v_j,h = Wuv_h (sum_j p_ij,h c_j)
+//
+// The kernels work on the latent side of both identities: a query head is first
+// carried into latent space (rank numbers), scores and the weighted sum run over
+// cached latents, and the head's value projection is applied once to the sum.  Scores,
+// softmax weights, the running maximum, sum and accumulator are float32.  A sink is
+// a learned score per head with no key and no value: it only enlarges the
+// denominator, once.  Without sinks (null) the softmax is the usual one.
+//
+// latent_attention_generic: one warp per (token, head), keys in chunks of 32 from
+// the window's start in increasing position, so the order of every addition depends
+// only on the token's position: the float32 path, and the path of sizes the tiled
+// kernel does not take.
+#include "common.cuh"
+
+namespace ifx {
+
+// ------------------------------------------------------------- norm + append
+// One warp per token: c = x / rms(x) * w over `rank` columns starting at column
+// `col0` of a row of `ld` elements; c goes to the cache at the token's position
+// (and, if `c_out` is given, to c_out[t, :] as well).
+template <typename T>
+__global__ void latent_norm_append_kernel(const T* __restrict__ rows, int ld, int col0, const float* __restrict__ w,
+                                          float eps, const int* __restrict__ positions,
+                                          const int* __restrict__ token_req, const int* __restrict__ req_slot,
+                                          const int* __restrict__ block_table, int max_blocks, int page_size,
+                                          int num_pages, T* __restrict__ pool, T* __restrict__ c_out, int num_tokens,
+                                          int rank) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= num_tokens) return;
+  const T* x = rows + (size_t)t * ld + col0;
+  float ss = 0.0f;
+  for (int e = lane; e < rank; e += 32) {
+    const float v = to_f32(x[e]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)rank + eps);
+  T* dst = nullptr;
+  if (pool != nullptr) {
+    const int pos = positions[t];
+    const int slot = req_slot[token_req[t]];
+    const int page = block_table[(size_t)slot * max_blocks + pos / page_size];
+    if (page >= 0 && page < num_pages) dst = pool + ((size_t)page * page_size + pos % page_size) * rank;
+  }
+  for (int e = lane; e < rank; e += 32) {
+    const T c = from_f32<T>(to_f32(x[e]) * r * w[e]);
+    if (dst) dst[e] = c;
+    if (c_out) c_out[(size_t)t * rank + e] = c;
+  }
+}
+
+// ------------------------------------------------------------------ attention
+constexpr int kLatentWarps = 4;
+
+// NR = ceil(rank / 32): latent elements a lane owns (e = lane + 32 i).
+template <typename T, int NR>
+__global__ void __launch_bounds__(kLatentWarps * 32) latent_attention_generic_kernel(
+    const T* __restrict__ q, int ldq, const T* __restrict__ w_uk, const T* __restrict__ w_uv,
+    const float* __restrict__ sinks, const T* __restrict__ pool, const int* __restrict__ block_table,
+    const int* __restrict__ positions, const int* __restrict__ token_req, const int* __restrict__ req_slot,
+    const int* __restrict__ rows, T* __restrict__ out, int num_tokens, int heads, int dim, int vdim, int rank,
+    int page_size, int max_blocks, int num_pages, int window, float scale) {
+  extern __shared__ float lat_s[];                       // per warp: `rank` floats (query in latent space, then the sum)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * kLatentWarps + warp;
+  if (item >= (long long)num_tokens * heads) return;
+  const int t = rows ? rows[item / heads] : (int)(item / heads), h = (int)(item % heads);
+  float* ql = lat_s + (size_t)warp * rank;
+  const int pos = positions[t];
+  const int slot = req_slot[token_req[t]];
+  const int* table = block_table + (size_t)slot * max_blocks;
+
+  // the query head in latent space: ql[e] = sum_d Wuk[h dim + d, e] q[d]
+  {
+    const T* qh = q + (size_t)t * ldq + (size_t)h * dim;
+    const T* wk = w_uk + (size_t)h * dim * rank;
+    float a[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) a[i] = 0.0f;
+    for (int d = 0; d < dim; ++d) {
+      const float qd = to_f32(qh[d]);
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int e = lane + 32 * i;
+        if (e < rank) a[i] = fmaf(to_f32(wk[(size_t)d * rank + e]), qd, a[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int e = lane + 32 * i;
+      if (e < rank) ql[e] = a[i];
+    }
+    __syncwarp();
+  }
+
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int end = pos + 1;
+  float m = -INFINITY, l = 0.0f;
+  float acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) acc[i] = 0.0f;
+
+  for (int base = first; base < end; base += 32) {
+    const int j = base + lane;
+    const bool valid = j < end;
+    float s = -INFINITY;
+    const T* crow = pool;
+    if (valid) {
+      int page = table[j / page_size];
+      if (page < 0 || page >= num_pages) page = 0;       // a broken table must not read outside the pool
+      crow = pool + ((size_t)page * page_size + j % page_size) * rank;
+      float dot = 0.0f;
+      for (int e = 0; e < rank; ++e) dot = fmaf(ql[e], to_f32(crow[e]), dot);
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float p = valid ? expf(s - m_new) : 0.0f;
+    const float corr = expf(m - m_new);                  // m = -inf at the start: exp(-inf) = 0
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) acc[i] *= corr;
+    const int count = min(32, end - base);
+    for (int jj = 0; jj < count; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const T* cr = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, (unsigned long long)crow, jj));
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int e = lane + 32 * i;
+        if (e < rank) acc[i] = fmaf(pj, to_f32(cr[e]), acc[i]);
+      }
+    }
+  }
+  if (sinks != nullptr) {                                // the sink joins the denominator only
+    const float sk = sinks[h];
+    const float m_new = fmaxf(m, sk);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sk - m_new);
+#pragma unroll
+    for (int i = 0; i < NR; ++i) acc[i] *= corr;
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int e = lane + 32 * i;
+    if (e < rank) ql[e] = acc[i] * inv;
+  }
+  __syncwarp();
+  // the head's values: o[v] = sum_e Wuv[h vdim + v, e] ql[e]
+  T* orow = out + ((size_t)t * heads + h) * vdim;
+  const T* wv = w_uv + (size_t)h * vdim * rank;
+  for (int v0 = 0; v0 < vdim; v0 += 32) {
+    const int v = v0 + lane;
+    if (v < vdim) {
+      const T* wr = wv + (size_t)v * rank;
+      float o = 0.0f;
+      for (int e = 0; e < rank; ++e) o = fmaf(to_f32(wr[e]), ql[e], o);
+      orow[v] = from_f32<T>(o);
+    }
+  }
+}
+
+}  // namespace ifx
+
+using namespace ifx;
+
+extern "C" {
+
+int ifx_latent_norm_append(const void* rows, int ld, int col0, const float* w, float eps, const int* positions,
+                           const int* token_req, const int* req_slot, const int* block_table, int max_blocks,
+                           int page_size, int num_pages, void* pool, void* c_out, int T, int rank, int dtype,
+                           cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rank <= 0 || ld < col0 + rank || col0 < 0) return IFX_E_BADARG;
+  if (pool != nullptr && (page_size <= 0 || max_blocks <= 0 || block_table == nullptr)) return IFX_E_BADARG;
+  const int warps = 4;
+  const unsigned blocks = (unsigned)((T + warps - 1) / warps);
+  if (dtype == IFX_DT_F32)
+    latent_norm_append_kernel<float><<<blocks, warps * 32, 0, stream>>>(
+        (const float*)rows, ld, col0, w, eps, positions, token_req, req_slot, block_table, max_blocks, page_size,
+        num_pages, (float*)pool, (float*)c_out, T, rank);
+  else if (dtype == IFX_DT_BF16)
+    latent_norm_append_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)rows, ld, col0, w, eps, positions, token_req, req_slot, block_table, max_blocks,
+        page_size, num_pages, (__nv_bfloat16*)pool, (__nv_bfloat16*)c_out, T, rank);
+  else
+    return IFX_E_DTYPE;
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+int ifx_latent_attention_max_rank() { return 1024; }
+
+int ifx_latent_attention_generic(const void* q, int ldq, const void* w_uk, const void* w_uv, const float* sinks,
+                                 const void* pool, const int* block_table, const int* positions,
+                                 const int* token_req, const int* req_slot, const int* rows, void* out,
+                                 int num_tokens, int heads, int dim, int vdim, int rank, int page_size,
+                                 int max_blocks, int num_pages, int window, float scale, int dtype,
+                                 cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (heads <= 0 || dim <= 0 || vdim <= 0 || rank <= 0 || page_size <= 0 || max_blocks <= 0 || ldq < heads * dim)
+    return IFX_E_BADARG;
+  if (rank > 1024) return IFX_E_TOOBIG;
+  const long long items = (long long)num_tokens * heads;
+  const unsigned blocks = (unsigned)((items + kLatentWarps - 1) / kLatentWarps);
+  const size_t smem = (size_t)kLatentWarps * rank * sizeof(float);
+#define IFX_LAUNCH(TT, NR)                                                                                         \
+  latent_attention_generic_kernel<TT, NR><<<blocks, kLatentWarps * 32, smem, stream>>>(                            \
+      (const TT*)q, ldq, (const TT*)w_uk, (const TT*)w_uv, sinks, (const TT*)pool, block_table, positions,         \
+      token_req, req_slot, rows, (TT*)out, num_tokens, heads, dim, vdim, rank, page_size, max_blocks, num_pages,   \
+      window, scale)
+#define IFX_BY_RANK(TT)                          \
+  do {                                           \
+    if (rank <= 64) IFX_LAUNCH(TT, 2);           \
+    else if (rank <= 128) IFX_LAUNCH(TT, 4);     \
+    else if (rank <= 256) IFX_LAUNCH(TT, 8);     \
+    else if (rank <= 512) IFX_LAUNCH(TT, 16);    \
+    else IFX_LAUNCH(TT, 32);                     \
+  } while (0)
+  if (dtype == IFX_DT_F32) IFX_BY_RANK(float);
+  else if (dtype == IFX_DT_BF16) IFX_BY_RANK(__nv_bfloat16);
+  else return IFX_E_DTYPE;
+#undef IFX_BY_RANK
+#undef IFX_LAUNCH
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

@@ -140,7 +140,8 @@ class CudaKernels:
                    "ifx_attention_prefill_tcgen05", "ifx_attention_prefill_tcgen05_supports", "ifx_attention_decode_max_splits",
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows",
-                   "ifx_gemm_tcgen05"):
+                   "ifx_gemm_tcgen05", "ifx_postnorm_add_rmsnorm", "ifx_concat_cast", "ifx_xielu", "ifx_softcap",
+                   "ifx_short_conv", "ifx_latent_norm_append", "ifx_latent_attention_generic"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         with torch.cuda.device(self.device):
@@ -693,6 +694,104 @@ class CudaKernels:
             _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot),
             _ptr(rows), _ptr(out), count, nq, nkv, d, *common, _DT[q.dtype], _stream()), "attention")
         self.launches += 1
+
+    # ------------------------------------------- layers that norm a sublayer's output
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None):
+        """x += y / rms(y) * w_post (x float32, in place).  With `w_next`, also returns the next norm of the
+        updated rows, x / rms(x) * w_next in `out_dtype`: sum and both norms in one kernel."""
+        y = self.materialize(y)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape,
+              "postnorm_add: x must be float32 and y of its shape")
+        _need(w_post.dtype == torch.float32 and (w_next is None or w_next.dtype == torch.float32),
+              "postnorm_add: norm weights must be float32")
+        T, H = x.shape
+        out = None if w_next is None else torch.empty((T, H), dtype=out_dtype or y.dtype, device=x.device)
+        _check(self.lib.ifx_postnorm_add_rmsnorm(
+            _ptr(x), _ptr(y), _ptr(w_post), ctypes.c_float(eps_post), _ptr(w_next), ctypes.c_float(eps_next), _ptr(out),
+            T, H, _DT[y.dtype], _DT[(out_dtype or y.dtype)], _stream()), "postnorm_add")
+        self.launches += 1
+        return out
+
+    def concat_cast(self, a, b, dtype):
+        """[a; b] along the columns, from two float32 tensors into `dtype`."""
+        _need(a.dtype == torch.float32 and b.dtype == torch.float32 and a.shape == b.shape and a.is_contiguous()
+              and b.is_contiguous(), "concat_cast: two float32 tensors of one shape")
+        T, H = a.shape
+        out = torch.empty((T, 2 * H), dtype=dtype, device=a.device)
+        _check(self.lib.ifx_concat_cast(_ptr(a), _ptr(b), _ptr(out), T, H, _DT[dtype], _stream()), "concat_cast")
+        self.launches += 1
+        return out
+
+    def xielu(self, z, a_pos, a_neg):
+        """a_pos z^2 + z/2 above zero, a_neg (e^z - 1 - z) + z/2 below, element by element, in float32."""
+        _need(z.is_contiguous(), "xielu: contiguous input")
+        out = torch.empty_like(z)
+        _check(self.lib.ifx_xielu(_ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), ctypes.c_float(a_pos),
+                                  ctypes.c_float(a_neg), _DT[z.dtype], _stream()), "xielu")
+        self.launches += 1
+        return out
+
+    def softcap(self, logits, cap):
+        """logits <- cap tanh(logits / cap), in place (float32)."""
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "softcap: float32 logits")
+        _check(self.lib.ifx_softcap(_ptr(logits), ctypes.c_longlong(logits.numel()), ctypes.c_float(cap), _stream()),
+               "softcap")
+        self.launches += 1
+
+    def short_conv(self, h, w, taps, state, index, ctx):
+        """h + causal depthwise convolution of h over each request's tokens; `state[:, index]` (float32
+        [slots, convolutions, taps - 1, channels]) brings the inputs before the step and takes the last ones."""
+        T, C = h.shape
+        _need(h.is_contiguous() and w.dtype == torch.float32 and tuple(w.shape) == (C, taps), "short_conv: bad operands")
+        st_ptr, stride = ctypes.c_void_p(0), 0
+        if taps > 1:
+            _need(state is not None and state.dtype == torch.float32 and state.is_contiguous()
+                  and tuple(state.shape[2:]) == (taps - 1, C) and 0 <= index < state.shape[1],
+                  "short_conv: the state does not fit the convolution")
+            stride = state.shape[1] * (taps - 1) * C
+            st_ptr = ctypes.c_void_p(state.data_ptr() + 4 * index * (taps - 1) * C)
+        out = torch.empty_like(h)
+        _check(self.lib.ifx_short_conv(_ptr(h), _ptr(w), st_ptr, ctypes.c_longlong(stride), _ptr(ctx.token_req),
+                                       _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out), T, ctx.num_requests, C,
+                                       taps, int(ctx.max_span > 1), _DT[h.dtype], _stream()), "short_conv")
+        self.launches += 1 + int(taps > 1 and ctx.max_span > 1)
+        return out
+
+    # -------------------------------------------------------- latent attention
+    def latent_attention_sections(self, ctx):
+        return {}
+
+    def latent_norm_append(self, rows, col0, rank, w, eps, ctx, cache):
+        """The latent of every token: columns col0 .. col0 + rank of `rows`, RMS-normed with weight `w`,
+        written to the cache at the token's position."""
+        T, ld = rows.shape
+        kv, table = cache.kv, cache.block_table
+        _need(kv is not None and table is not None and kv.dtype == rows.dtype, "latent_norm_append: no cache of the run's dtype")
+        _need(kv.shape[1] == 1 and kv.shape[2] == 1 and kv.shape[4] == rank, "latent_norm_append: the cache is not one latent plane")
+        write = bool(cache.writes)
+        _check(self.lib.ifx_latent_norm_append(
+            _ptr(rows), ld, col0, _ptr(w), ctypes.c_float(eps), _ptr(ctx.positions), _ptr(ctx.token_req),
+            _ptr(ctx.req_slot), _ptr(table), table.shape[1], cache.page_size, kv.shape[0], _ptr(kv if write else None),
+            _ptr(None), T, rank, _DT[rows.dtype], _stream()), "latent_norm_append")
+        self.launches += 1
+
+    def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache):
+        """Attention over cached latents (see csrc/latent_attention.cu).  `q_rows`: [T, >= heads * dim], the
+        queries in its first columns.  Returns [T, heads * vdim]."""
+        T, ldq = q_rows.shape
+        kv, table = cache.kv, cache.block_table
+        _need(kv is not None and table is not None and kv.dtype == q_rows.dtype, "latent_attention: no cache of the run's dtype")
+        _need(q_rows.is_contiguous() and w_uk.is_contiguous() and w_uv.is_contiguous(), "latent_attention: contiguous operands")
+        _need(tuple(w_uk.shape) == (heads * dim, rank) and tuple(w_uv.shape) == (heads * vdim, rank),
+              "latent_attention: the up-projections do not fit the sizes")
+        out = torch.empty((T, heads * vdim), dtype=q_rows.dtype, device=q_rows.device)
+        _check(self.lib.ifx_latent_attention_generic(
+            _ptr(q_rows), ldq, _ptr(w_uk), _ptr(w_uv), _ptr(sinks), _ptr(kv), _ptr(table), _ptr(ctx.positions),
+            _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(None), _ptr(out), T, heads, dim, vdim, rank, cache.page_size,
+            table.shape[1], kv.shape[0], 0 if window is None else int(window), ctypes.c_float(scale), _DT[q_rows.dtype],
+            _stream()), "latent_attention")
+        self.launches += 1
+        return out
 
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):

@@ -12,7 +12,7 @@ from typing import Dict, List
 import torch
 
 from ..config.plan import ModelPlan
-from ..parts import build_part
+from ..parts import build_part, settle_pending
 from ..weights.loader import TensorSpec
 
 
@@ -102,13 +102,15 @@ class Model:
         schedule entry.  Returns float32 logits [len(ctx.logit_rows), vocab]."""
         k = ctx.kernels
         x = self.embedding.forward(ctx)                       # float32 [T, hidden]
+        if self.plan.keeps_embedding_output:                  # a second gather: x itself is updated in place
+            ctx.embedding_output = self.embedding.forward(ctx)
         pending = None
         for entry in self.plan.schedule:
+            ctx.entry = entry
             x, pending = self.layers[entry.layer].block.forward(x, pending, ctx, caches.view(entry))
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=x.device)
-        if pending is not None:
-            k.residual_add(x, pending)
+        settle_pending(x, pending, ctx)
         rows = k.gather_rows(x, ctx.logit_rows)               # float32 [R, hidden]
         h = self.final_norm.forward(rows, None, ctx)
         return self.lm_head.forward(h, ctx)

@@ -1,7 +1,9 @@
 """The parts layers are made of.  Importing the package registers the built-in kinds."""
-from .base import (Block, FeedForward, KVCacheSpec, Mixer, Norm, Part, PositionEncoding, RotaryTable,
-                   StateSpec, WeightBuffers, build_part, register_part, registered_parts)
-from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (registration)
+from .base import (Block, FeedForward, KVCacheSpec, Mixer, Norm, NormedDelta, Part, PositionEncoding, RotaryTable,
+                   StateSpec, StreamMerge, TimeConv, WeightBuffers, build_part, register_part, registered_parts,
+                   settle_pending)
+from . import attention, block, conv, embedding, latent_attention, mlp, norm, rope  # noqa: F401  (registration)
 
-__all__ = ["Block", "FeedForward", "KVCacheSpec", "Mixer", "Norm", "Part", "PositionEncoding",
-           "RotaryTable", "StateSpec", "WeightBuffers", "build_part", "register_part", "registered_parts"]
+__all__ = ["Block", "FeedForward", "KVCacheSpec", "Mixer", "Norm", "NormedDelta", "Part", "PositionEncoding",
+           "RotaryTable", "StateSpec", "StreamMerge", "TimeConv", "WeightBuffers", "build_part", "register_part",
+           "registered_parts", "settle_pending"]

@@ -9,6 +9,8 @@ does its work through the kernel table of the step (`ctx.kernels`).
     PositionEncoding  rotary() -> RotaryTable or None
     Mixer             cache_spec() / state_spec(); forward(h, ctx, cache) -> y
     FeedForward       forward(h, ctx) -> y
+    TimeConv          state_rows; forward(h, ctx, state, index) -> h'
+    StreamMerge       forward(x, x0, repeat, ctx) -> x'
     Block             sub_parts (name -> role); forward(x, pending, ctx, cache) -> (x, pending)
 
 `x` is the float32 residual stream [tokens, hidden]; `h` and `y` are in the dtype
@@ -34,10 +36,13 @@ from ..weights.loader import TensorSpec
 @dataclass(frozen=True)
 class KVCacheSpec:
     """What a mixer stores per token: keys and values of `num_kv_heads` heads of
-    `head_dim`; `window` None keeps every key, an integer only the last `window`."""
+    `head_dim`; `window` None keeps every key, an integer only the last `window`.
+    `planes` 2 stores keys and values; 1 stores one vector per head that serves as
+    both (a latent from which keys and values are made)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -45,6 +50,28 @@ class StateSpec:
     """What a mixer stores per request, whatever the request's length."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+class NormedDelta:
+    """A sublayer's output that joins the residual stream only after a norm of its own:
+    x += y / rms(y) * weight.  A block hands it on as `pending`, so that whatever norms x next
+    does both in one kernel (`ctx.kernels.postnorm_add`); `add_to` does the sum alone."""
+
+    def __init__(self, y, weight: torch.Tensor, eps: float):
+        self.y, self.weight, self.eps = y, weight, float(eps)
+
+    def add_to(self, x: torch.Tensor, ctx) -> None:
+        ctx.kernels.postnorm_add(x, self.y, self.weight, self.eps)
+
+
+def settle_pending(x: torch.Tensor, pending, ctx) -> None:
+    """x += pending, whatever kind of delta it is."""
+    if pending is None:
+        return
+    if isinstance(pending, NormedDelta):
+        pending.add_to(x, ctx)
+    else:
+        ctx.kernels.residual_add(x, pending)
 
 
 @dataclass
@@ -153,6 +180,25 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TimeConv(Part):
+    """A convolution over a request's tokens on each channel.  `state_rows` inputs per
+    channel are a request's state between steps (None: nothing is kept)."""
+
+    state_rows: Optional[int] = None
+
+    def forward(self, h: torch.Tensor, ctx, state: Optional[torch.Tensor], index: int) -> torch.Tensor:
+        """`state`: float32 [slots, convolutions of the layer, state_rows, channels]; `index` says which
+        of the layer's convolutions this one is."""
+        raise NotImplementedError
+
+
+class StreamMerge(Part):
+    """Makes a new residual stream from the present one and the embedding output."""
+
+    def forward(self, x: torch.Tensor, x0: torch.Tensor, repeat: int, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block(Part):
     """An arrangement of parts around the residual stream.  A block kind says which
     parts it arranges (`sub_parts`: name -> role); the layer's spec must bring exactly
@@ -183,6 +229,7 @@ class Block(Part):
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {
     "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "lm_head": {},
+    "conv": {}, "merge": {},
 }
 
 

@@ -17,19 +17,20 @@ from .base import Part, register_part
 
 @register_part("embedding", "embedding")
 class Embedding(Part):
-    """params: vocab_size, hidden_size."""
+    """params: vocab_size, hidden_size, tensor_name (default `weight`)."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.tensor_name = str(spec.params.get("tensor_name", "weight"))
         self.table = None
 
     def param_specs(self):
-        return {"weight": TensorSpec((self.vocab, self.hidden))}
+        return {self.tensor_name: TensorSpec((self.vocab, self.hidden))}
 
     def load(self, tensors, dtype, device):
-        self.table = tensors["weight"].to(device=device, dtype=dtype).contiguous()
+        self.table = tensors[self.tensor_name].to(device=device, dtype=dtype).contiguous()
 
     def forward(self, ctx):
         return ctx.kernels.embed(self.table, ctx.token_ids, self.vocab)
@@ -37,13 +38,17 @@ class Embedding(Part):
 
 @register_part("lm_head", "lm_head")
 class LMHead(Part):
-    """params: vocab_size, hidden_size, tied."""
+    """params: vocab_size, hidden_size, tied, softcap (None, or c: logits become c tanh(logits / c))."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.tied = bool(spec.params.get("tied", False))
+        cap = spec.params.get("softcap")
+        self.softcap = None if cap is None else float(cap)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"lm_head: softcap must be positive, got {self.softcap}")
         self.weight = None
 
     def param_specs(self):
@@ -59,4 +64,7 @@ class LMHead(Part):
 
     def forward(self, h, ctx):
         """h: normed rows [R, hidden] -> float32 logits [R, vocab]."""
-        return ctx.kernels.linear(h, self.weight, out_dtype=torch.float32)
+        logits = ctx.kernels.linear(h, self.weight, out_dtype=torch.float32)
+        if self.softcap is not None:
+            ctx.kernels.softcap(logits, self.softcap)
+        return logits

@@ -11,19 +11,23 @@ from .base import Norm, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps."""
+    """params: size, eps, unit_offset (the stored weight is the distance from one: y = x / rms * (1 + w);
+    default False), tensor_name (default `weight`)."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.unit_offset = bool(spec.params.get("unit_offset", False))
+        self.tensor_name = str(spec.params.get("tensor_name", "weight"))
         self.weight = None
 
     def param_specs(self):
-        return {"weight": TensorSpec((self.size,), init="ones")}
+        return {self.tensor_name: TensorSpec((self.size,), init="zeros" if self.unit_offset else "ones")}
 
     def load(self, tensors, dtype, device):
-        self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
+        w = tensors[self.tensor_name].to(device=device, dtype=torch.float32)
+        self.weight = (w + 1.0 if self.unit_offset else w).contiguous()      # the kernels multiply by this
 
     def forward(self, x, delta, ctx, lazy=False):
         if lazy and hasattr(ctx.kernels, "prenorm"):

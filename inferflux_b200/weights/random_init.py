@@ -112,7 +112,10 @@ def random_tensors(expected: Dict[str, TensorSpec], seed: int, dtype=torch.bfloa
             else:
                 t = torch.ones(spec.shape, dtype=dtype, device=dev)
         elif spec.init == "zeros":
-            t = torch.zeros(spec.shape, dtype=dtype, device=dev)
+            if norm_jitter:
+                t = counter_normal(spec.shape, seed, name, 0.0, norm_jitter, dtype, dev)
+            else:
+                t = torch.zeros(spec.shape, dtype=dtype, device=dev)
         else:
             raise ValueError(f"unknown init {spec.init!r} for {name}")
         out[name] = t

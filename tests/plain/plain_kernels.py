@@ -121,6 +121,70 @@ class PlainKernels:
                 out[t, h] = (p @ V[:, g, :]).to(q.dtype)
         return out.reshape(T, nq * d)
 
+    # ------------------------------------------- layers that norm a sublayer's output
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None):
+        ya = y.to(self.acc)
+        x += (ya * torch.rsqrt((ya * ya).mean(-1, keepdim=True) + eps_post) * w_post.to(self.acc)).to(torch.float32)
+        if w_next is None:
+            return None
+        return self.rmsnorm(x, w_next, eps_next, out_dtype or y.dtype)
+
+    def concat_cast(self, a, b, dtype):
+        return torch.cat([a, b], dim=-1).to(dtype)
+
+    def xielu(self, z, a_pos, a_neg):
+        za = z.to(self.acc)
+        neg = a_neg * (torch.expm1(torch.clamp(za, max=0.0)) - za) + 0.5 * za
+        return torch.where(za > 0, a_pos * za * za + 0.5 * za, neg).to(z.dtype)
+
+    def softcap(self, logits, cap):
+        logits.copy_(cap * torch.tanh(logits.to(self.acc) / cap))
+
+    def short_conv(self, h, w, taps, state, index, ctx):
+        ha, wa = h.to(self.acc), w.to(self.acc)
+        out = ha * (1.0 + wa[:, taps - 1])
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
+        for r in range(ctx.num_requests):
+            lo, hi = cu[r], cu[r + 1]
+            if taps == 1:
+                continue
+            old = state[slots[r], index].to(self.acc)                       # [taps - 1, C]
+            seq = torch.cat([old, ha[lo:hi]], dim=0)                        # inputs from taps - 1 before the span
+            for k in range(1, taps):
+                out[lo:hi] += wa[:, taps - 1 - k] * seq[taps - 1 - k:taps - 1 - k + (hi - lo)]
+            state[slots[r], index] = seq[-(taps - 1):].to(state.dtype)
+        return out.to(h.dtype)
+
+    # -------------------------------------------------------- latent attention
+    def latent_norm_append(self, rows, col0, rank, w, eps, ctx, cache):
+        xa = rows[:, col0:col0 + rank].to(self.acc)
+        c = xa * torch.rsqrt((xa * xa).mean(-1, keepdim=True) + eps) * w.to(self.acc)
+        if cache.writes:
+            P, pos = cache.page_size, ctx.positions.long()
+            slot = ctx.req_slot.long()[ctx.token_req.long()]
+            page = cache.block_table[slot, pos // P].long()
+            cache.kv[page, 0, 0, pos % P, :] = c.to(cache.kv.dtype)
+
+    def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache):
+        T, P = q_rows.shape[0], cache.page_size
+        q = q_rows[:, :heads * dim].to(self.acc).view(T, heads, dim)
+        uk, uv = w_uk.to(self.acc).view(heads, dim, rank), w_uv.to(self.acc).view(heads, vdim, rank)
+        out = torch.empty((T, heads, vdim), dtype=q_rows.dtype, device=q_rows.device)
+        pos_all, req_all, slots = ctx.positions.tolist(), ctx.token_req.tolist(), ctx.req_slot.tolist()
+        for t in range(T):
+            pos, slot = pos_all[t], slots[req_all[t]]
+            first = max(0, pos - window + 1) if window else 0
+            keys = torch.arange(first, pos + 1, device=q_rows.device)
+            pages = cache.block_table[slot, keys // P].long()
+            C = cache.kv[pages, 0, 0, keys % P, :].to(self.acc)            # [n, rank]
+            for h in range(heads):
+                s = (C @ (uk[h].t() @ q[t, h])) * scale
+                if sinks is not None:
+                    s = torch.cat([s, sinks[h:h + 1].to(self.acc)])
+                p = torch.softmax(s, dim=0)[:keys.numel()]
+                out[t, h] = (uv[h] @ (p @ C)).to(q_rows.dtype)
+        return out.reshape(T, heads * vdim)
+
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):
         return torch.argmax(logits, dim=-1).to(torch.int32)
