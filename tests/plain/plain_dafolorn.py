@@ -89,16 +89,21 @@ def dense_ff(h, t, prefix):
     return xielu(z, act[0], act[1]) @ t[prefix + "down"].T
 
 
-def layer(x, t, i, spec, eps):
+def layer(x, t, i, spec, eps, conv=True):
+    """`conv` False: the design without its input convolutions (a configuration that names none)."""
     p = f"l{i}."
-    h = short_conv(offset_norm(x, t[p + "norm1"], eps), t[p + "canon1"])
+    h = offset_norm(x, t[p + "norm1"], eps)
+    if conv:
+        h = short_conv(h, t[p + "canon1"])
     if spec["type"] != "latent_attention":
         raise ValueError(spec["type"])
     x = x + offset_norm(latent_attention(h, t, p + "mix.", spec["mixer"], eps), t[p + "norm1b"], eps)
     if spec.get("mlp") is not None:
         if spec["mlp"]["kind"] != "dense":
             raise ValueError(spec["mlp"]["kind"])
-        h = short_conv(offset_norm(x, t[p + "norm2"], eps), t[p + "canon2"])
+        h = offset_norm(x, t[p + "norm2"], eps)
+        if conv:
+            h = short_conv(h, t[p + "canon2"])
         x = x + offset_norm(dense_ff(h, t, p + "mlp."), t[p + "norm2b"], eps)
     return x
 
@@ -125,7 +130,7 @@ def forward(config, tensors, tokens, dtype=F, want_layers=False):
     for i, rep, first in run_order(config):
         if first:
             x = torch.cat([x, x0], dim=-1) @ t["loop.in"].T + t["loop.step"][rep]
-        x = layer(x, t, i, config["layers"][i], eps)
+        x = layer(x, t, i, config["layers"][i], eps, conv=bool(config.get("canon")))
         streams.append(x)
     logits = offset_norm(x, t["final.norm"], eps) @ t["embed"].T
     cap = config.get("logit_softcap")
