@@ -438,6 +438,210 @@ def run_reference(args, pk):
     return 0
 
 
+# ---------------------------------------------------------------- another design beside the closest existing model
+# Dafolorn at sizes that resemble real layers, and the Qwen2 shape of equal size: the same width, heads, vocabulary and
+# number of layer runs (2 + 6 looped 4 times + 2 = 28); the feed-forward has two matrices instead of three, so it is
+# 1.5 times as wide; key/value heads of 128 against a latent of 256 per token; a window of 4,096.
+DESIGN_SHAPES = {
+    "1.5b": dict(width=1536, heads=12, ff=13440, vocab=151936, qwen="1.5b"),
+    "7b": dict(width=3584, heads=28, ff=28416, vocab=152064, qwen="7b"),
+}
+
+
+def dafolorn_config(shape, window=4096, rank=256):
+    from inferflux_b200.config import DafolornConfig
+    s = DESIGN_SHAPES[shape]
+    layer = {"type": "latent_attention",
+             "mixer": {"heads": s["heads"], "dim": 128, "vdim": 128, "kv_rank": rank, "mask": {"size": window},
+                       "scale": 128 ** -0.5},
+             "mlp": {"kind": "dense", "ff": s["ff"]}}
+    return DafolornConfig.from_dict({"architecture": "Dafolorn", "vocab": s["vocab"], "width": s["width"],
+                                     "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "logit_softcap": 30.0,
+                                     "loop": {"start": 2, "stop": 8, "times": 4}, "layers": [layer] * 10})
+
+
+def dafolorn_step_bytes(cfg, batch, context):
+    """Bytes a decode step must read: every matrix of every layer run, the merges, the head, the cached latents."""
+    w, total = cfg.width, 0
+    runs = cfg.run_order()
+    for i, _rep, first in runs:
+        m, mlp = cfg.layers[i]["mixer"], cfg.layers[i]["mlp"]
+        q, v, r = m["heads"] * m["dim"], m["heads"] * m["vdim"], m["kv_rank"]
+        total += 2 * (w * (q + r) + q * r + v * r + v * w + (2 * w * mlp["ff"] if mlp else 0))
+        total += 2 * w * 2 * w if first else 0
+        keys = min(context, (m.get("mask") or {}).get("size") or context)
+        total += batch * keys * r * 2
+    return total + 2 * cfg.vocab * w
+
+
+def dafolorn_prefill_flops(cfg, tokens):
+    w, total = cfg.width, 0
+    for i, _rep, first in cfg.run_order():
+        m, mlp = cfg.layers[i]["mixer"], cfg.layers[i]["mlp"]
+        q, v, r = m["heads"] * m["dim"], m["heads"] * m["vdim"], m["kv_rank"]
+        total += 2 * tokens * (w * (q + r) + q * r + v * r + v * w + (2 * w * mlp["ff"] if mlp else 0) + (2 * w * w if first else 0))
+        total += 4 * m["heads"] * r * (tokens * (tokens + 1) // 2)       # scores and sums over latents (window >= tokens)
+    return total + 2 * cfg.vocab * w
+
+
+def _event_times(fn, reps=15, warm=3):
+    """Median ms of fn() alone on the device: captured into a CUDA graph (so that the host's time between its
+    launches does not count) and replayed with the L2 flushed (a 512 MB write) before every timed replay."""
+    import torch
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda:0")
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    times = []
+    for i in range(warm + reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warm:
+            times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def design_kernels(kernels, dcfg, qcfg, pk, batch, context, tokens):
+    """The new design's kernels beside the like kernels of the closest model, each alone at the layer's sizes:
+    microseconds and the fraction of its roofline (HBM bytes, or tensor FLOPs where those take longer)."""
+    import torch
+    from inferflux_b200.cache import CacheManager
+    from inferflux_b200.config import ScheduleEntry
+    from inferflux_b200.engine.batch import StepContext, StepEntry
+    from inferflux_b200.parts import KVCacheSpec
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    m = dcfg.layers[0]["mixer"]
+    H, dk, dv, r, w = m["heads"], m["dim"], m["vdim"], m["kv_rank"], dcfg.width
+    nq, nkv, d = qcfg.num_attention_heads, qcfg.num_key_value_heads, qcfg.head_dim
+    page, out = 16, {}
+
+    def row(name, ms, bytes_=0, flops=0):
+        roof = max(bytes_ / hbm, flops / tf)
+        out[name] = {"us": round(ms * 1000, 1), "roofline_us": round(roof * 1e6, 1), "frac": round(roof / (ms * 1e-3), 3),
+                     "bound": "hbm" if bytes_ / hbm >= flops / tf else "tensor"}
+
+    def ctx_for(cache, spans):
+        entries, starts, slots = [], [], []
+        for rid, n in spans:
+            if rid not in cache:
+                cache.add_request(rid)
+            start = cache.length(rid)
+            cache.reserve(rid, start + n)
+            entries.append(StepEntry(rid, [0] * n, []))
+            starts.append(start)
+            slots.append(cache.slot(rid))
+        ctx = StepContext.build(kernels, bf, dev, entries, starts, slots, cache.drain_table_updates())
+        for g, (idx, pg) in zip(cache.groups, ctx.table_updates):
+            kernels.scatter_i32(g.table, idx, pg)
+        for (rid, n), start in zip(spans, starts):
+            cache.commit(rid, start + n)
+        return ctx
+
+    for what, spans_a, spans_b in (("decode", [(f"r{i}", context - 1) for i in range(batch)], [(f"r{i}", 1) for i in range(batch)]),
+                                   ("prefill", [], [("p", tokens)])):
+        T = sum(n for _r, n in spans_b)
+        keys = sum((context if what == "decode" else (n * (n + 1)) // 2) for _r, n in spans_b)
+        pages = (batch * context if what == "decode" else tokens) // page + 2 * batch + 2
+        # the new design: one latent plane
+        cache = CacheManager([(KVCacheSpec(1, r, None, planes=1), None)], page_size=page, num_pages=pages, max_seqs=batch,
+                             max_seq_len=max(context, tokens) + 16, dtype=bf, device=dev)
+        cache.groups[0].pool.normal_()
+        if spans_a:
+            ctx_for(cache, spans_a)
+        ctx = ctx_for(cache, spans_b)
+        view = cache.view(ScheduleEntry(0, 0))
+        q_rows = torch.randn(T, H * dk + r, device=dev).to(bf)
+        w_uk, w_uv = (torch.randn(H * dk, r, device=dev) * 0.05).to(bf), (torch.randn(H * dv, r, device=dev) * 0.05).to(bf)
+        sinks = torch.zeros(H, device=dev)
+        ms = _event_times(lambda: kernels.latent_attention(q_rows, w_uk, w_uv, sinks, H, dk, dv, r, None, dk ** -0.5, ctx, view))
+        row(f"latent attention, {what} (3 launches: into latent space, tiles, values)", ms,
+            bytes_=(batch * context if what == "decode" else tokens) * r * 2 + 2 * T * H * (dk + r + r + dv),
+            flops=4 * H * r * keys + 2 * T * H * r * (dk + dv))
+        del cache
+        # the closest model: keys and values of nkv heads
+        cache = CacheManager([(KVCacheSpec(nkv, d, None), None)], page_size=page, num_pages=pages, max_seqs=batch,
+                             max_seq_len=max(context, tokens) + 16, dtype=bf, device=dev)
+        cache.groups[0].pool.normal_()
+        if spans_a:
+            ctx_for(cache, spans_a)
+        ctx = ctx_for(cache, spans_b)
+        view = cache.view(ScheduleEntry(0, 0))
+        q = torch.randn(T, nq * d, device=dev).to(bf)
+        ms = _event_times(lambda: kernels.attention(q, nq, nkv, d, None, d ** -0.5, ctx, view))
+        row(f"attention of the closest model, {what}", ms,
+            bytes_=(batch * context if what == "decode" else tokens) * 2 * nkv * d * 2 + 4 * T * nq * d, flops=4 * nq * d * keys)
+        del cache
+        # rows: sum + norms; convolution; activation
+        x = torch.randn(T, w, device=dev)
+        y = torch.randn(T, w, device=dev).to(bf)
+        wn = torch.ones(w, device=dev)
+        ms = _event_times(lambda: kernels.postnorm_add(x, y, wn, 1e-6, wn, 1e-6, bf))
+        row(f"sum of the normed delta + next norm, {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        ms = _event_times(lambda: kernels.add_rmsnorm(x, y, wn, 1e-6, bf))
+        row(f"sum + norm of the closest model, {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        state = torch.zeros(batch, 2, 3, w, device=dev)
+        wc = torch.randn(w, 4, device=dev)
+        ms = _event_times(lambda: kernels.short_conv(y, wc, 4, state, 0, ctx))
+        row(f"short convolution, {T} rows", ms, bytes_=T * w * 4)
+        ff = dcfg.layers[0]["mlp"]["ff"]
+        z = torch.randn(T, ff, device=dev).to(bf)
+        ms = _event_times(lambda: kernels.xielu(z, 0.69, 1.19))
+        row(f"xIELU, {T} rows", ms, bytes_=T * ff * 4)
+        gu = torch.randn(T, 2 * qcfg.intermediate_size, device=dev).to(bf)
+        ms = _event_times(lambda: kernels.silu_mul(gu))
+        row(f"SiLU * up of the closest model, {T} rows", ms, bytes_=T * qcfg.intermediate_size * 6)
+    kernels.check_errors()
+    return out
+
+
+def run_design(args, pk):
+    """`--design dafolorn`: decode and prefill throughput of the design at real layer sizes beside the Qwen2 shape of
+    equal size, and its kernels beside the like kernels, one JSON line."""
+    import torch
+    page, batch, context = 16, args.batch, min(args.context, 4096)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    result = {"metric": "decode and prefill tokens/s of another design beside the closest model at equal size",
+              "design": args.design, "dtype": "bf16", "n_gpus": 1, "data": "synthetic: random weights, uniform random token ids",
+              "batch": batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "peaks": pk["source"], "shapes": {}}
+    kernels_table = None
+    for shape in ([args.shape] if args.shape in DESIGN_SHAPES else sorted(DESIGN_SHAPES)):
+        entry = {}
+        for name in ("dafolorn", "qwen2"):
+            cfg = dafolorn_config(shape) if name == "dafolorn" else qwen7b_config(DESIGN_SHAPES[shape]["qwen"])
+            if args.layers and name == "qwen2":
+                cfg.num_hidden_layers = args.layers
+            longest = context + 4 * (warmup + 3 * steps) + 16 + batch
+            engine = _engine(cfg, page, batch, longest)
+            r = time_decode(engine, cfg, batch, steps, warmup, repeats=3, context=context, e2e=False)
+            pre_ms = time_prefill(engine, cfg, PREFILL_TOKENS, warmup=2, reps=5)
+            if name == "dafolorn":
+                step_bytes, flops = dafolorn_step_bytes(cfg, batch, r["ctx"]), dafolorn_prefill_flops(cfg, PREFILL_TOKENS)
+            else:
+                step_bytes = weight_bytes(cfg, batch) + batch * r["ctx"] * kv_bytes_per_token(cfg)
+                flops = prefill_flops(cfg, PREFILL_TOKENS)
+            entry[name] = {"decode_tok_s": round(batch * 1000.0 / r["dev_ms"], 1), "decode_ms_per_step": round(r["dev_ms"], 3),
+                           "decode_hbm_frac": round(step_bytes / (r["dev_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 3),
+                           "launches_per_step": round(r["launches"], 1),
+                           "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 2),
+                           "prefill_tensor_frac": round(flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 3)}
+            if name == "dafolorn" and kernels_table is None:
+                kernels_table = design_kernels(engine.kernels, cfg, qwen7b_config(DESIGN_SHAPES[shape]["qwen"]), pk, batch,
+                                               context, PREFILL_TOKENS)
+                entry["kernels"] = kernels_table
+            del engine
+            torch.cuda.empty_cache()
+        result["shapes"][shape] = entry
+    print(json.dumps(result))
+    return 0
+
+
 def _engine(cfg, page, slots, longest, pages=None, chunk=2048):
     import torch
     from inferflux_b200 import Engine
@@ -471,11 +675,16 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true", help="skip the PyTorch baseline and the 1.5B-shape points")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the 2,048-token prefill and print a short line (for profiling prefill)")
+    ap.add_argument("--design", default="", choices=["", "dafolorn"],
+                    help="instead of the headline numbers: this design at real layer sizes beside the Qwen2 shape of equal "
+                         "size (decode and prefill tokens/s, and its kernels beside the like kernels); --shape picks one size")
     args = ap.parse_args()
 
     pk = peaks()
     if args.impl == "reference":
         return run_reference(args, pk)
+    if args.design:
+        return run_design(args, pk)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

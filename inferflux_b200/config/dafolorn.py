@@ -53,6 +53,10 @@ class DafolornConfig:
     architecture = "Dafolorn"
     model_type = "dafolorn"
 
+    @property
+    def vocab_size(self) -> int:            # the name generic callers use
+        return self.vocab
+
     # ------------------------------------------------------------------ reading
     @classmethod
     def from_dict(cls, raw: dict) -> "DafolornConfig":

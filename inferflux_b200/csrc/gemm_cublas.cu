@@ -63,3 +63,27 @@ extern "C" int ifx_gemm_cublas_bf16(const void* A, const void* W, void* C, int M
   if (st != CUBLAS_STATUS_SUCCESS) return 1000 + (int)st;
   return 0;
 }
+
+// A batch of small products that share their shapes, e.g. one per attention head:
+//   w_is_nk = 1:  C_b[M, N] = A_b[M, K] . W_b[N, K]^T      (W_b stored [N, K], rows ldw apart)
+//   w_is_nk = 0:  C_b[M, N] = A_b[M, K] . W_b[K, N]        (W_b stored [K, N], rows ldw apart)
+// A_b, W_b, C_b start stride_a, stride_w, stride_c elements after the batch before; rows of A and C are lda and
+// ldc elements apart, so heads may lie side by side in one row.  bfloat16 in and out, float32 accumulation.
+extern "C" int ifx_gemm_cublas_bf16_batched(const void* A, long long lda, long long stride_a, const void* W,
+                                            long long ldw, long long stride_w, void* C, long long ldc,
+                                            long long stride_c, int M, int N, int K, int batch, int w_is_nk,
+                                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0) return IFX_E_BADARG;
+  cublasHandle_t h;
+  int rc = get_handle(&h);
+  if (rc) return rc;
+  if (cublasSetStream(h, stream) != CUBLAS_STATUS_SUCCESS) return IFX_E_BADARG;
+  const float alpha = 1.0f, beta = 0.0f;
+  cublasStatus_t st = cublasGemmStridedBatchedEx(
+      h, w_is_nk ? CUBLAS_OP_T : CUBLAS_OP_N, CUBLAS_OP_N, N, M, K, &alpha, W, CUDA_R_16BF, (int)ldw, stride_w, A,
+      CUDA_R_16BF, (int)lda, stride_a, &beta, C, CUDA_R_16BF, (int)ldc, stride_c, batch, CUBLAS_COMPUTE_32F,
+      CUBLAS_GEMM_DEFAULT);
+  if (st != CUBLAS_STATUS_SUCCESS) return 1000 + (int)st;
+  return 0;
+}

@@ -127,6 +127,7 @@ class CudaKernels:
     """Kernel table on one CUDA device."""
 
     name = "cuda-sm100a"
+    fuses_single_token_conv = True     # postnorm_add takes a short convolution for steps of single tokens
 
     def __init__(self, device="cuda"):
         if not torch.cuda.is_available():
@@ -141,9 +142,13 @@ class CudaKernels:
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows",
                    "ifx_gemm_tcgen05", "ifx_postnorm_add_rmsnorm", "ifx_concat_cast", "ifx_xielu", "ifx_softcap",
-                   "ifx_short_conv", "ifx_latent_norm_append", "ifx_latent_attention_generic"):
+                   "ifx_short_conv", "ifx_latent_norm_append", "ifx_latent_attention_generic", "ifx_latent_attention_mma",
+                   "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
+        self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
+        # latent attention on the tensor-core tiles (0: the per-token kernel, for comparisons)
+        self.latent_tiles = os.environ.get("INFERFLUX_B200_LATENT_TILES", "1") != "0"
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
         if os.environ.get("INFERFLUX_B200_CARVEOUT", "") != "":    # for measurements: -1 leaves the split to the driver
@@ -696,19 +701,38 @@ class CudaKernels:
         self.launches += 1
 
     # ------------------------------------------- layers that norm a sublayer's output
-    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None):
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, conv=None):
         """x += y / rms(y) * w_post (x float32, in place).  With `w_next`, also returns the next norm of the
-        updated rows, x / rms(x) * w_next in `out_dtype`: sum and both norms in one kernel."""
-        y = self.materialize(y)
-        _need(x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape,
+        updated rows, x / rms(x) * w_next in `out_dtype`: sum and both norms in one kernel.  `conv` =
+        (weight [hidden, taps], taps, state, index, ctx), allowed when every request of the step brings one token
+        (`ctx.max_span == 1`): the rows come back as h + conv(h) over time, and the state has moved on."""
+        splits = 1
+        if isinstance(y, PartialSum):                      # the slices are added in the same pass
+            _need(tuple(y.shape) == tuple(x.shape), "postnorm_add: partial sums do not match x")
+            out_dtype = out_dtype or y.dtype
+            y, splits = y.parts, y.splits
+        _need(x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and tuple(y.shape[-2:]) == tuple(x.shape),
               "postnorm_add: x must be float32 and y of its shape")
         _need(w_post.dtype == torch.float32 and (w_next is None or w_next.dtype == torch.float32),
               "postnorm_add: norm weights must be float32")
         T, H = x.shape
         out = None if w_next is None else torch.empty((T, H), dtype=out_dtype or y.dtype, device=x.device)
+        cw, taps, st_ptr, stride, treq, rslot = None, 0, ctypes.c_void_p(0), 0, None, None
+        if conv is not None:
+            cw, taps, state, index, ctx = conv
+            _need(w_next is not None and ctx.max_span == 1 and tuple(cw.shape) == (H, taps) and cw.dtype == torch.float32,
+                  "postnorm_add: the convolution is fused only into steps of single tokens")
+            if taps > 1:
+                _need(state is not None and state.dtype == torch.float32 and state.is_contiguous()
+                      and tuple(state.shape[2:]) == (taps - 1, H) and 0 <= index < state.shape[1],
+                      "postnorm_add: the state does not fit the convolution")
+                stride = state.shape[1] * (taps - 1) * H
+                st_ptr = ctypes.c_void_p(state.data_ptr() + 4 * index * (taps - 1) * H)
+            treq, rslot = ctx.token_req, ctx.req_slot
         _check(self.lib.ifx_postnorm_add_rmsnorm(
             _ptr(x), _ptr(y), _ptr(w_post), ctypes.c_float(eps_post), _ptr(w_next), ctypes.c_float(eps_next), _ptr(out),
-            T, H, _DT[y.dtype], _DT[(out_dtype or y.dtype)], _stream()), "postnorm_add")
+            T, H, _DT[y.dtype], _DT[(out_dtype or y.dtype)], splits, _ptr(cw), taps, st_ptr, ctypes.c_longlong(stride),
+            _ptr(treq), _ptr(rslot), _stream()), "postnorm_add")
         self.launches += 1
         return out
 
@@ -724,10 +748,13 @@ class CudaKernels:
 
     def xielu(self, z, a_pos, a_neg):
         """a_pos z^2 + z/2 above zero, a_neg (e^z - 1 - z) + z/2 below, element by element, in float32."""
+        splits, out_dtype = 1, z.dtype
+        if isinstance(z, PartialSum):                      # a K-split product: the slices are added first, in the same pass
+            out_dtype, splits, z = z.dtype, z.splits, z.parts
         _need(z.is_contiguous(), "xielu: contiguous input")
-        out = torch.empty_like(z)
-        _check(self.lib.ifx_xielu(_ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), ctypes.c_float(a_pos),
-                                  ctypes.c_float(a_neg), _DT[z.dtype], _stream()), "xielu")
+        out = torch.empty(tuple(z.shape[-2:]), dtype=out_dtype, device=z.device)
+        _check(self.lib.ifx_xielu(_ptr(z), _ptr(out), ctypes.c_longlong(out.numel()), ctypes.c_float(a_pos),
+                                  ctypes.c_float(a_neg), _DT[z.dtype], _DT[out_dtype], splits, _stream()), "xielu")
         self.launches += 1
         return out
 
@@ -758,8 +785,34 @@ class CudaKernels:
         return out
 
     # -------------------------------------------------------- latent attention
+    LATENT_TILE = 64           # tokens per work item of the tiled latent attention kernel
+
     def latent_attention_sections(self, ctx):
-        return {}
+        """latent.items[P, 4] = (slot, first flat token, tokens, first position): every span in pieces of up
+        to 64 tokens; a decoded token is an item of one."""
+        items, base = [], 0
+        for (start, n), slot in zip(ctx.spans, ctx.slots_host):
+            for off in range(0, n, self.LATENT_TILE):
+                items.extend((int(slot), base + off, min(self.LATENT_TILE, n - off), start + off))
+            base += n
+        return {"latent.items": items}
+
+    def linear_heads(self, a, w, heads, k, n, w_is_nk):
+        """One small product per head, heads side by side in the rows of `a` [T, >= heads * k]:
+        out[:, h n:(h + 1) n] = a[:, h k:(h + 1) k] . W_h^T with W_h = w[h n:(h + 1) n] of [n, k] (w_is_nk), or
+        a[:, h k:(h + 1) k] . W_h with W_h = w[h k:(h + 1) k] of [k, n].  bfloat16, through the library."""
+        T, lda = a.shape
+        _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous(),
+              "linear_heads: contiguous bfloat16 operands")
+        _need(tuple(w.shape) == ((heads * n, k) if w_is_nk else (heads * k, n)) and lda >= heads * k,
+              "linear_heads: shapes do not fit")
+        out = torch.empty((T, heads * n), dtype=torch.bfloat16, device=a.device)
+        ldw = k if w_is_nk else n
+        _check(self.lib.ifx_gemm_cublas_bf16_batched(
+            _ptr(a), _LL(lda), _LL(k), _ptr(w), _LL(ldw), _LL(k * n), _ptr(out), _LL(heads * n), _LL(n), T, n, k, heads,
+            int(bool(w_is_nk)), _stream()), "linear_heads")
+        self.library_calls += 1
+        return out
 
     def latent_norm_append(self, rows, col0, rank, w, eps, ctx, cache):
         """The latent of every token: columns col0 .. col0 + rank of `rows`, RMS-normed with weight `w`,
@@ -784,6 +837,9 @@ class CudaKernels:
         _need(q_rows.is_contiguous() and w_uk.is_contiguous() and w_uv.is_contiguous(), "latent_attention: contiguous operands")
         _need(tuple(w_uk.shape) == (heads * dim, rank) and tuple(w_uv.shape) == (heads * vdim, rank),
               "latent_attention: the up-projections do not fit the sizes")
+        if (self.latent_tiles and q_rows.dtype == torch.bfloat16 and self.lib.ifx_latent_attention_mma_supports(rank)
+                and dim % 8 == 0 and vdim % 8 == 0 and ldq % 8 == 0):
+            return self._latent_attention_tiles(q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache)
         out = torch.empty((T, heads * vdim), dtype=q_rows.dtype, device=q_rows.device)
         _check(self.lib.ifx_latent_attention_generic(
             _ptr(q_rows), ldq, _ptr(w_uk), _ptr(w_uv), _ptr(sinks), _ptr(kv), _ptr(table), _ptr(ctx.positions),
@@ -792,6 +848,35 @@ class CudaKernels:
             _stream()), "latent_attention")
         self.launches += 1
         return out
+
+    def _latent_attention_tiles(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache):
+        """bfloat16: queries into latent space (a product per head), the tensor-core kernel over cached latents
+        with all heads of a token tile in one block, the value projection per head on the weighted latents."""
+        T = q_rows.shape[0]
+        kv, table = cache.kv, cache.block_table
+        if "latent.items" not in ctx.extra:                # a step context built without the mixer as a provider
+            vals = self.latent_attention_sections(ctx)["latent.items"]
+            ctx.extra["latent.items"] = torch.tensor(vals, dtype=torch.int32, device=q_rows.device)
+            ctx.extra_len["latent.items"] = len(vals)
+        items, num_items = ctx.extra["latent.items"], ctx.extra_len["latent.items"] // 4
+        ql = self.linear_heads(q_rows, w_uk, heads, dim, rank, w_is_nk=False)               # [T, heads * rank]
+        win = 0 if window is None else int(window)
+        splits = 1
+        if ctx.max_span == 1:                              # decoded tokens only: cut the keys so that the SMs fill
+            max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
+            blocks = num_items * -(-heads // 64)                 # about four warps a SM, at least two key tiles each
+            splits = max(1, min(592 // max(1, blocks), max_keys // 64, 64))
+        ws = None
+        if splits > 1:
+            ws = torch.empty(int(self.lib.ifx_latent_attention_mma_workspace(T * heads, rank, splits)), dtype=torch.uint8,
+                             device=q_rows.device)
+        olat = torch.empty((T, heads * rank), dtype=torch.bfloat16, device=q_rows.device)
+        _check(self.lib.ifx_latent_attention_mma(
+            _ptr(ql), _ptr(kv), _ptr(table), _ptr(items), num_items, int(min(self.LATENT_TILE, ctx.max_span)), _ptr(sinks),
+            _ptr(olat), _ptr(ws), T, heads, rank, cache.page_size, table.shape[1], kv.shape[0], win, ctypes.c_float(scale),
+            splits, _stream()), "latent_attention (tiles)")
+        self.launches += 1 + int(splits > 1)
+        return self.linear_heads(olat, w_uv, heads, rank, vdim, w_is_nk=True)               # [T, heads * vdim]
 
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):

@@ -3,6 +3,7 @@
 //
 //   postnorm_add_rmsnorm   x += y / rms(y) * w_post           (x float32, in place)
 //                          h  = x / rms(x) * w_next           (optional second stage)
+//                          y may arrive as the float32 partial sums [splits, rows, hidden] of a K-split product
 //   concat_cast            out[t] = [a[t]; b[t]] in the run's dtype, a and b float32
 //   xielu                  z -> a_pos z^2 + z/2 (z > 0), a_neg (e^z - 1 - z) + z/2 (z <= 0)
 //   softcap                v -> cap tanh(v / cap), float32 in place
@@ -13,35 +14,108 @@
 
 namespace ifx {
 
+// What a row that is its request's only token in the step needs for the short convolution behind the norm
+// (see short_conv.cu): its taps, and the request's state, which the row reads and moves on itself.
+struct SingleTokenConv {
+  const float* w;            // [hidden, taps], null: no convolution
+  float* state;              // this convolution's [taps - 1, hidden] of slot 0
+  long long slot_stride;     // floats from one slot to the next
+  const int* token_req;
+  const int* req_slot;
+  int taps;
+};
+
+// Few rows make this kernel a chain of round trips to memory, not a stream: everything a thread will need
+// that does not depend on a reduction (its first elements of x and of the norm weights) is asked for before
+// the first reduction, the slices of a K-split product are loaded in batches before they are added, and a
+// row gets 1,024 threads when there are few rows.
 template <typename TY, typename TO>
-__global__ void __launch_bounds__(256) postnorm_add_rmsnorm_kernel(
+__global__ void __launch_bounds__(1024) postnorm_add_rmsnorm_kernel(
     float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ w_post, float eps_post,
-    const float* __restrict__ w_next, float eps_next, TO* __restrict__ out, int hidden) {
+    const float* __restrict__ w_next, float eps_next, TO* __restrict__ out, int hidden, int splits,
+    size_t split_stride, SingleTokenConv conv) {
   extern __shared__ float row_s[];                       // the row, kept between the passes
   __shared__ float scratch[32];
   const size_t row = blockIdx.x;
   float* xr = x + row * hidden;
   const TY* yr = y + row * hidden;
+  constexpr int PRE = 2;                                 // elements per thread fetched ahead
+  float x_pre[PRE], wp_pre[PRE], wn_pre[PRE];
+#pragma unroll
+  for (int j = 0; j < PRE; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    x_pre[j] = i < hidden ? xr[i] : 0.0f;
+    wp_pre[j] = i < hidden ? w_post[i] : 0.0f;
+    wn_pre[j] = (i < hidden && out != nullptr) ? w_next[i] : 0.0f;
+  }
   float ss = 0.0f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = to_f32(yr[i]);
+    float v = to_f32(yr[i]);
+    int s = 1;
+    for (; s + 4 <= splits; s += 4) {                    // K-split partial sums: four loads in flight, added in split order
+      const float p0 = to_f32(yr[(size_t)s * split_stride + i]), p1 = to_f32(yr[(size_t)(s + 1) * split_stride + i]);
+      const float p2 = to_f32(yr[(size_t)(s + 2) * split_stride + i]), p3 = to_f32(yr[(size_t)(s + 3) * split_stride + i]);
+      v += p0; v += p1; v += p2; v += p3;
+    }
+    for (; s < splits; ++s) v += to_f32(yr[(size_t)s * split_stride + i]);
     row_s[i] = v;
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
   const float r1 = rsqrtf(ss / (float)hidden + eps_post);
   float ss2 = 0.0f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = xr[i] + row_s[i] * r1 * w_post[i];
+  auto add_row = [&](int i, float xi, float wi) {
+    const float v = xi + row_s[i] * r1 * wi;
     xr[i] = v;
     row_s[i] = v;
     ss2 = fmaf(v, v, ss2);
+  };
+#pragma unroll
+  for (int j = 0; j < PRE; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < hidden) add_row(i, x_pre[j], wp_pre[j]);
   }
+  for (int i = threadIdx.x + PRE * blockDim.x; i < hidden; i += blockDim.x) add_row(i, xr[i], w_post[i]);
   if (out == nullptr) return;
   ss2 = block_sum(ss2, scratch);
   const float r2 = rsqrtf(ss2 / (float)hidden + eps_next);
   TO* o = out + row * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<TO>(row_s[i] * r2 * w_next[i]);
+  if (conv.w == nullptr) {
+#pragma unroll
+    for (int j = 0; j < PRE; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) o[i] = from_f32<TO>(row_s[i] * r2 * wn_pre[j]);
+    }
+    for (int i = threadIdx.x + PRE * blockDim.x; i < hidden; i += blockDim.x) o[i] = from_f32<TO>(row_s[i] * r2 * w_next[i]);
+    return;
+  }
+  // h + conv(h) for a single token: the inputs before it are the state; afterwards the state ends with h
+  float* st = conv.state + (long long)conv.req_slot[conv.token_req[row]] * conv.slot_stride;
+  const int taps = conv.taps;
+  auto conv_one = [&](int i, float wn) {
+    const float* wc = conv.w + (size_t)i * taps;
+    float old[15], wk[15];                                               // the input k + 1 steps back, and its tap
+#pragma unroll
+    for (int k = 0; k < 15; ++k) {
+      old[k] = k < taps - 1 ? st[(size_t)(taps - 2 - k) * hidden + i] : 0.0f;
+      wk[k] = k < taps - 1 ? wc[taps - 2 - k] : 0.0f;
+    }
+    const float h = to_f32(from_f32<TO>(row_s[i] * r2 * wn));            // the convolution reads h in the run's dtype
+    float acc = fmaf(wc[taps - 1], h, h);
+#pragma unroll
+    for (int k = 0; k < 15; ++k)
+      if (k < taps - 1) {
+        acc = fmaf(wk[k], old[k], acc);
+        st[(size_t)(taps - 2 - k) * hidden + i] = k == 0 ? h : old[k - 1];
+      }
+    o[i] = from_f32<TO>(acc);
+  };
+#pragma unroll
+  for (int j = 0; j < PRE; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < hidden) conv_one(i, wn_pre[j]);
+  }
+  for (int i = threadIdx.x + PRE * blockDim.x; i < hidden; i += blockDim.x) conv_one(i, w_next[i]);
 }
 
 template <typename T>
@@ -59,10 +133,30 @@ __device__ __forceinline__ float xielu_f(float z, float a_pos, float a_neg) {
   return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
 }
 
-template <typename T>
-__global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ out, long long n, float a_pos, float a_neg) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    out[i] = from_f32<T>(xielu_f(to_f32(z[i]), a_pos, a_neg));
+// splits > 1: z is float32 [splits, n], the partial sums of a K-split product, added in split order first.
+template <typename TI, typename TO>
+__global__ void xielu_kernel(const TI* __restrict__ z, TO* __restrict__ out, long long n, float a_pos, float a_neg,
+                             int splits) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = to_f32(z[i]);
+    for (int s = 1; s < splits; ++s) v += to_f32(z[(long long)s * n + i]);
+    out[i] = from_f32<TO>(xielu_f(v, a_pos, a_neg));
+  }
+}
+
+// The same, eight bfloat16 (16 bytes) per thread and step, for element counts that are multiples of 8.
+__global__ void xielu_bf16x8_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ out, long long n8,
+                                    float a_pos, float a_neg) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    uint4 raw = reinterpret_cast<const uint4*>(z)[i];
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h2[k]);
+      h2[k] = __floats2bfloat162_rn(xielu_f(f.x, a_pos, a_neg), xielu_f(f.y, a_pos, a_neg));
+    }
+    reinterpret_cast<uint4*>(out)[i] = raw;
+  }
 }
 
 __global__ void softcap_kernel(float* __restrict__ v, long long n, float cap) {
@@ -82,21 +176,32 @@ using namespace ifx;
 extern "C" {
 
 // y_dtype: dtype of y; out_dtype: dtype of out (ignored when out is null: first stage only).
+// splits > 1: y is float32 [splits, T, hidden].
+// conv_w non-null (only for steps in which every request brings one token, and with `out`): the rows leave as
+// h + conv(h), with `conv_state` (this convolution's part of slot 0, slots conv_slot_stride floats apart) read and moved on.
 int ifx_postnorm_add_rmsnorm(float* x, const void* y, const float* w_post, float eps_post, const float* w_next,
-                             float eps_next, void* out, int T, int hidden, int y_dtype, int out_dtype,
-                             cudaStream_t stream) {
+                             float eps_next, void* out, int T, int hidden, int y_dtype, int out_dtype, int splits,
+                             const float* conv_w, int taps, float* conv_state, long long conv_slot_stride,
+                             const int* token_req, const int* req_slot, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hidden <= 0) return IFX_E_BADARG;
+  SingleTokenConv conv = {conv_w, conv_state, conv_slot_stride, token_req, req_slot, taps};
+  if (conv_w != nullptr && (out == nullptr || taps < 1 || taps > 16 || (taps > 1 && conv_state == nullptr) ||
+                            token_req == nullptr || req_slot == nullptr))
+    return IFX_E_BADARG;
+  if (hidden <= 0 || splits < 1 || (splits > 1 && y_dtype != IFX_DT_F32)) return IFX_E_BADARG;
+  const size_t split_stride = (size_t)T * hidden;
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return IFX_E_TOOBIG;
+  const int threads = (T <= 512 && hidden > 512) ? 1024 : 256;           // few rows: more threads a row
   if (out != nullptr && w_next == nullptr) return IFX_E_BADARG;
 #define IFX_LAUNCH(TY, TO)                                                                                         \
   do {                                                                                                             \
     auto kern = postnorm_add_rmsnorm_kernel<TY, TO>;                                                               \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    kern<<<T, 256, smem, stream>>>(x, (const TY*)y, w_post, eps_post, w_next, eps_next, (TO*)out, hidden);         \
+    kern<<<T, threads, smem, stream>>>(x, (const TY*)y, w_post, eps_post, w_next, eps_next, (TO*)out, hidden, splits,  \
+                                   split_stride, conv);                                                            \
   } while (0)
-  const int od = out == nullptr ? y_dtype : out_dtype;
+  const int od = out == nullptr ? IFX_DT_F32 : out_dtype;
   if (y_dtype == IFX_DT_F32 && od == IFX_DT_F32) IFX_LAUNCH(float, float);
   else if (y_dtype == IFX_DT_BF16 && od == IFX_DT_BF16) IFX_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (y_dtype == IFX_DT_F32 && od == IFX_DT_BF16) IFX_LAUNCH(float, __nv_bfloat16);
@@ -119,13 +224,22 @@ int ifx_concat_cast(const float* a, const float* b, void* out, int T, int hidden
   return 0;
 }
 
-int ifx_xielu(const void* z, void* out, long long n, float a_pos, float a_neg, int dtype, cudaStream_t stream) {
+int ifx_xielu(const void* z, void* out, long long n, float a_pos, float a_neg, int in_dtype, int out_dtype, int splits,
+              cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (dtype == IFX_DT_F32)
-    xielu_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)z, (float*)out, n, a_pos, a_neg);
-  else if (dtype == IFX_DT_BF16)
-    xielu_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>((const __nv_bfloat16*)z, (__nv_bfloat16*)out, n,
-                                                                      a_pos, a_neg);
+  if (splits < 1 || (splits > 1 && in_dtype != IFX_DT_F32)) return IFX_E_BADARG;
+  if (in_dtype == IFX_DT_F32 && out_dtype == IFX_DT_F32)
+    xielu_kernel<float, float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)z, (float*)out, n, a_pos, a_neg, splits);
+  else if (in_dtype == IFX_DT_BF16 && out_dtype == IFX_DT_BF16 && n % 8 == 0 && (uintptr_t)z % 16 == 0 &&
+           (uintptr_t)out % 16 == 0)
+    xielu_bf16x8_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)z, (__nv_bfloat16*)out, n / 8,
+                                                                  a_pos, a_neg);
+  else if (in_dtype == IFX_DT_BF16 && out_dtype == IFX_DT_BF16)
+    xielu_kernel<__nv_bfloat16, __nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)z, (__nv_bfloat16*)out, n, a_pos, a_neg, splits);
+  else if (in_dtype == IFX_DT_F32 && out_dtype == IFX_DT_BF16)
+    xielu_kernel<float, __nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>((const float*)z, (__nv_bfloat16*)out, n,
+                                                                             a_pos, a_neg, splits);
   else return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();
   return 0;

@@ -56,6 +56,106 @@ __global__ void short_conv_kernel(const T* __restrict__ h, const float* __restri
   }
 }
 
+// The same for up to 4 taps and channel counts that are multiples of 16 bytes' worth of elements: a thread owns
+// VEC consecutive channels (one 16-byte load per input row) and walks kConvRows consecutive tokens, so that the
+// chain of metadata loads (token -> request -> span and slot) is paid once per request a block meets, not per element.
+constexpr int kConvRows = 4;
+
+template <typename T> struct ConvVec;
+template <> struct ConvVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct ConvVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h2[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_vec_kernel(
+    const T* __restrict__ h, const float* __restrict__ w, float* __restrict__ state, long long state_slot_stride,
+    const int* __restrict__ token_req, const int* __restrict__ req_slot, const int* __restrict__ cu_seqlens,
+    T* __restrict__ out, int num_tokens, int channels, int taps, int inline_single) {
+  constexpr int V = ConvVec<T>::N;
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c0 >= channels) return;
+  float wr[V][4];                                        // wr[v][k]: the tap of the input k steps back
+#pragma unroll
+  for (int v = 0; v < V; ++v)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) wr[v][k] = k < taps ? w[(size_t)(c0 + v) * taps + (taps - 1 - k)] : 0.0f;
+  const int t_end = min(num_tokens, (int)(blockIdx.x + 1) * kConvRows);
+  int r_at = -1, first = 0, n = 0;
+  float* st = nullptr;
+  for (int t = blockIdx.x * kConvRows; t < t_end; ++t) {
+    const int r = token_req[t];
+    if (r != r_at) {
+      r_at = r;
+      first = cu_seqlens[r];
+      n = cu_seqlens[r + 1] - first;
+      st = state ? state + (long long)req_slot[r] * state_slot_stride : nullptr;
+    }
+    const int i = t - first;
+    float in[4][V];                                      // in[k]: the input k steps back
+    ConvVec<T>::load(h + (size_t)t * channels + c0, in[0]);
+#pragma unroll
+    for (int k = 1; k < 4; ++k) {
+      if (k < taps) {
+        if (k <= i) {
+          ConvVec<T>::load(h + (size_t)(t - k) * channels + c0, in[k]);
+        } else {
+          const float* cell = st + (size_t)((taps - 1) - (k - i)) * channels + c0;
+#pragma unroll
+          for (int v = 0; v < V; v += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(cell + v);
+            in[k][v] = a.x; in[k][v + 1] = a.y; in[k][v + 2] = a.z; in[k][v + 3] = a.w;
+          }
+        }
+      }
+    }
+    float acc[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      acc[v] = fmaf(wr[v][0], in[0][v], in[0][v]);
+#pragma unroll
+      for (int k = 1; k < 4; ++k)
+        if (k < taps) acc[v] = fmaf(wr[v][k], in[k][v], acc[v]);
+    }
+    ConvVec<T>::store(out + (size_t)t * channels + c0, acc);
+    if (inline_single && n == 1 && st != nullptr) {      // the request's only token: it moves the state on itself
+#pragma unroll
+      for (int k = 1; k < 4; ++k)
+        if (k < taps) {
+          float* cell = st + (size_t)(taps - 1 - k) * channels + c0;
+#pragma unroll
+          for (int v = 0; v < V; v += 4)
+            *reinterpret_cast<float4*>(cell + v) = make_float4(in[k - 1][v], in[k - 1][v + 1], in[k - 1][v + 2], in[k - 1][v + 3]);
+        }
+    }
+  }
+}
+
 // New state of request r: the last taps - 1 entries of (old state ++ the span's inputs).
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ h, float* __restrict__ state,
@@ -101,10 +201,20 @@ int ifx_short_conv(const void* h, const float* w, float* state, long long state_
   const unsigned gy = (unsigned)((channels + threads - 1) / threads);
   if (gy > 65535u) return IFX_E_TOOBIG;
   dim3 grid((unsigned)T, gy), sgrid((unsigned)R, gy);
+  const int vec = dtype == IFX_DT_F32 ? 4 : 8;
+  const bool wide = taps <= 4 && channels % vec == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                    (state == nullptr || ((uintptr_t)state % 16 == 0 && state_slot_stride % 4 == 0));
+  const int vthreads = channels / vec >= 256 ? 256 : ((channels / vec + 31) / 32) * 32;
+  dim3 vgrid((unsigned)((T + kConvRows - 1) / kConvRows), wide ? (unsigned)((channels / vec + vthreads - 1) / vthreads) : 1u);
 #define IFX_LAUNCH(TT)                                                                                              \
   do {                                                                                                              \
-    short_conv_kernel<TT><<<grid, threads, 0, stream>>>((const TT*)h, w, state, state_slot_stride, token_req,       \
-                                                         req_slot, cu_seqlens, (TT*)out, channels, taps, 1);        \
+    if (wide)                                                                                                       \
+      short_conv_vec_kernel<TT><<<vgrid, vthreads, 0, stream>>>((const TT*)h, w, state, state_slot_stride,          \
+                                                                token_req, req_slot, cu_seqlens, (TT*)out, T,       \
+                                                                channels, taps, 1);                                 \
+    else                                                                                                            \
+      short_conv_kernel<TT><<<grid, threads, 0, stream>>>((const TT*)h, w, state, state_slot_stride, token_req,     \
+                                                           req_slot, cu_seqlens, (TT*)out, channels, taps, 1);      \
     if (taps > 1 && any_long)                                                                                       \
       short_conv_state_kernel<TT><<<sgrid, threads, 0, stream>>>((const TT*)h, state, state_slot_stride, req_slot,  \
                                                                  cu_seqlens, channels, taps, 1);                    \

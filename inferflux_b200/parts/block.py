@@ -90,6 +90,10 @@ class SandwichBlock(Block):
     def _sublayer_input(self, x, pending, norm, conv, index, ctx, cache):
         k = ctx.kernels
         if isinstance(pending, NormedDelta):
+            if conv is not None and ctx.max_span == 1 and getattr(k, "fuses_single_token_conv", False):
+                # decoded tokens only: sum, both norms and the convolution (its history is all state) in one kernel
+                return k.postnorm_add(x, pending.y, pending.weight, pending.eps, norm.weight, norm.eps, ctx.dtype,
+                                      conv=(conv.weight, conv.taps, cache.state, index, ctx))
             h = k.postnorm_add(x, pending.y, pending.weight, pending.eps, norm.weight, norm.eps, ctx.dtype)
         else:
             h = norm.forward(x, pending, ctx)

@@ -96,8 +96,8 @@ class LatentAttention(Mixer):
     # --------------------------------------------------------------------- forward
     def forward(self, h, ctx, cache):
         k = ctx.kernels
-        q_dkv = k.linear(h, self.w_q_dkv)                                   # [T, H dk + rank]
+        q_dkv = k.materialize(k.linear(h, self.w_q_dkv, allow_partial=True))   # [T, H dk + rank]
         k.latent_norm_append(q_dkv, self.heads * self.dk, self.rank, self.latent_norm, self.eps, ctx, cache)
         a = k.latent_attention(q_dkv, self.w_uk, self.w_uv, self.sinks, self.heads, self.dk, self.dv, self.rank,
                                self.window, self.scale, ctx, cache)         # [T, H dv]
-        return k.linear(a, self.w_o)
+        return k.linear(a, self.w_o, allow_partial=True)

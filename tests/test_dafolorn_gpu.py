@@ -68,6 +68,14 @@ def test_postnorm_add_and_next_norm(cuda_kernels, dtype, tol, H):
     xs = x.to(DEV).clone()
     assert cuda_kernels.postnorm_add(xs, y.to(DEV), (1 + wb).to(DEV), 1e-5) is None
     assert float((xs.cpu().double() - want_x).abs().max()) < 1e-5 * float(want_x.abs().max())
+    # y as the partial sums of a K-split product: added in the same pass
+    from inferflux_b200.csrc.ops import PartialSum
+    parts = _rnd(3, T, H, seed=5, scale=0.5)
+    parts[2] = y.float() - parts[0] - parts[1]
+    xp = x.to(DEV).clone()
+    hp = cuda_kernels.postnorm_add(xp, PartialSum(parts.to(DEV), dtype), (1 + wb).to(DEV), 1e-5, (1 + wn).to(DEV), 1e-3)
+    assert hp.dtype == dtype and float((xp.cpu().double() - want_x).abs().max()) < 1e-5 * float(want_x.abs().max())
+    assert float((hp.cpu().double() - want_h).abs().max()) < tol * float(want_h.abs().max())
     one = x[:1].to(DEV).clone()                                                   # a row's result does not depend on the others
     cuda_kernels.postnorm_add(one, y[:1].to(DEV), (1 + wb).to(DEV), 1e-5)
     assert torch.equal(one, xs[:1])
@@ -81,6 +89,11 @@ def test_xielu_softcap_concat(cuda_kernels, dtype, tol):
     got = cuda_kernels.xielu(z.to(DEV), sp(p), 0.5 + sp(q)).cpu().double()
     want = P.xielu(z.double(), p, q)
     assert float(((got - want).abs() / (1 + want.abs())).max()) < tol
+    from inferflux_b200.csrc.ops import PartialSum
+    parts = _rnd(4, 4, 333, seed=15, scale=2.0)
+    got = cuda_kernels.xielu(PartialSum(parts.to(DEV), dtype), sp(p), 0.5 + sp(q)).cpu()
+    want = P.xielu(parts.double().sum(0), p, q)
+    assert got.dtype == dtype and float(((got.double() - want).abs() / (1 + want.abs())).max()) < tol
     logits = _rnd(5, 1001, seed=6, scale=40.0)
     dev = logits.to(DEV).clone()
     cuda_kernels.softcap(dev, 12.5)
@@ -126,10 +139,11 @@ def test_short_conv_over_steps_and_requests(cuda_kernels, dtype, tol, taps):
 
 # ------------------------------------------------------------------ latent attention
 
-def _attention_case(kernels, dtype, window, sink, H=3, dk=40, dv=24, r=40, n=420, page=16, seed=0):
+def _attention_case(kernels, dtype, window, sink, H=3, dk=40, dv=24, r=40, n=420, page=16, seed=0, decode_only=False):
     """Latents through the norm-and-append kernel into pages, queries planted so that single keys stand
     out at a window's two sides, at page borders, among the first tokens and far back; the requests
-    are a decoded token, a two-token portion and a longer portion, all in one step."""
+    are a decoded token, a two-token portion and a longer portion, all in one step (or, `decode_only`,
+    three decoded tokens of requests of different lengths)."""
     from inferflux_b200.cache import CacheManager
     from inferflux_b200.config import ScheduleEntry
     from inferflux_b200.parts import KVCacheSpec
@@ -138,57 +152,84 @@ def _attention_case(kernels, dtype, window, sink, H=3, dk=40, dv=24, r=40, n=420
     w_uk, w_uv = _rnd(H * dk, r, seed=seed + 3, scale=0.4).to(dtype), _rnd(H * dv, r, seed=seed + 4, scale=0.3).to(dtype)
     sinks = _rnd(H, seed=seed + 5, scale=2.0) if sink else None
     W = window or n
-    tested = {"dec": [n - 1], "two": [n - 2, n - 1], "long": list(range(n - 50, n))}
-    lat = lambda i: rows[i, H * dk:].double()
-    for i in (n - 1, n - 2, n - 17, n - 33, n - 50):                      # plant: the key's latent points along the query's
+    if decode_only:                                                       # request -> (tokens before the step, tokens after)
+        spans_of = {"dec": (n - 1, n), "two": (n - 31, n - 30), "long": (n // 2, n // 2 + 1)}
+    else:
+        spans_of = {"dec": (n - 1, n), "two": (n - 2, n), "long": (n - 50, n)}
+    planted = sorted({e - 1 for _h, e in spans_of.values()} | {n - 17, n - 33, n - 50})
+    for i in planted:                                                     # plant: the key's latent points along the query's
         for head, j in ((0, i - W + 1), (1, i - W), (2, 3), (0, (i // page) * page), (1, (i // page) * page - 1)):
+            head %= H
             if 0 <= j < i:
                 ql = w_uk.double()[head * dk:(head + 1) * dk].T @ rows[i, head * dk:(head + 1) * dk].double()
-                rows[j, H * dk:] = (ql / ql.norm() * math.sqrt(r) * lat(j).norm() / math.sqrt(r) * 3.0).to(dtype)
+                rows[j, H * dk:] = (ql / ql.norm() * 3.0).to(dtype)
     c = P.plain_weight_norm(rows[:, H * dk:].double(), g.double(), 1e-6)
     c = c.to(dtype).double()                                              # what the cache holds
     scale = 1.7 / math.sqrt(dk)
     cache = CacheManager([(KVCacheSpec(1, r, window, planes=1), None)], page_size=page, num_pages=3 * (n // page + 1),
                          max_seqs=4, max_seq_len=512, dtype=dtype, device=DEV)
     view = lambda: cache.view(ScheduleEntry(0, 0))
-    heads = {"dec": n - 1, "two": n - 2, "long": n - 50}
-    spans = [(rid, head) for rid, head in heads.items()]                  # first the prefixes, in one step
+    spans = [(rid, head) for rid, (head, _e) in spans_of.items()]         # first the prefixes, in one step
     ctx, starts = _step_ctx(kernels, dtype, cache, spans)
     kernels.latent_norm_append(torch.cat([rows[:m] for _r, m in spans]).to(DEV), H * dk, r, g.to(DEV), 1e-6, ctx, view())
     _commit(cache, spans, starts)
-    spans = [(rid, n - head) for rid, head in heads.items()]
+    spans = [(rid, e - head) for rid, (head, e) in spans_of.items()]
     ctx, starts = _step_ctx(kernels, dtype, cache, spans)
-    step_rows = torch.cat([rows[heads[rid]:] for rid, _m in spans]).to(DEV).contiguous()
+    step_rows = torch.cat([rows[head:e] for head, e in spans_of.values()]).to(DEV).contiguous()
     kernels.latent_norm_append(step_rows, H * dk, r, g.to(DEV), 1e-6, ctx, view())
     got = kernels.latent_attention(step_rows, w_uk.to(DEV), w_uv.to(DEV), None if sinks is None else sinks.to(DEV),
                                    H, dk, dv, r, window, scale, ctx, view()).cpu().double()
     _commit(cache, spans, starts)
+    kernels.check_errors()
     worst, row = 0.0, 0
-    for rid, m in spans:
-        for i in range(heads[rid], n):
+    for rid, (head, end) in spans_of.items():
+        for i in range(head, end):
             lo = max(0, i - W + 1)
             for a in range(H):
                 q = rows[i, a * dk:(a + 1) * dk].double()
                 s = (c[lo:i + 1] @ (w_uk.double()[a * dk:(a + 1) * dk].T @ q)) * scale
                 p = P.windowed_sink_softmax(s, sinks[a].double() if sink else -1e30)
                 want = w_uv.double()[a * dv:(a + 1) * dv] @ (p @ c[lo:i + 1])
-                if i in tested[rid]:
-                    worst = max(worst, float((got[row, a * dv:(a + 1) * dv] - want).abs().max()) / (1e-3 + float(want.abs().max())))
+                worst = max(worst, float((got[row, a * dv:(a + 1) * dv] - want).abs().max()) / (1e-3 + float(want.abs().max())))
             row += 1
     return worst
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+# bfloat16 takes the tensor-core tiles for latents that are multiples of 16 (up to 256), else the per-token kernel
+# (bfloat16: the planted keys have scores of 20 and more, so that rounding a query or a latent moves a weight by percents)
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 5e-2)])
 @pytest.mark.parametrize("window,sink", [(37, True), (16, True), (17, False), (1, True), (None, True), (300, False)])
-def test_latent_attention_kernels_planted_keys(cuda_kernels, dtype, tol, window, sink):
-    assert _attention_case(cuda_kernels, dtype, window, sink) < tol
+@pytest.mark.parametrize("r", [40, 64])
+def test_latent_attention_kernels_planted_keys(cuda_kernels, dtype, tol, window, sink, r):
+    assert _attention_case(cuda_kernels, dtype, window, sink, r=r) < tol
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("sizes", [(1, 8, 8, 24), (5, 16, 40, 72), (2, 64, 64, 128), (4, 24, 16, 200), (2, 128, 128, 512)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 5e-2)])
+@pytest.mark.parametrize("sizes", [(1, 8, 8, 24), (5, 16, 40, 72), (2, 64, 64, 128), (4, 24, 16, 200), (2, 128, 128, 512),
+                                   (6, 24, 40, 48), (16, 32, 32, 256), (70, 8, 8, 32), (3, 16, 16, 16), (64, 8, 16, 80)])
 def test_latent_attention_kernels_other_sizes(cuda_kernels, dtype, tol, sizes):
     H, dk, dv, r = sizes
     assert _attention_case(cuda_kernels, dtype, 45, True, H=H, dk=dk, dv=dv, r=r, n=140, seed=20) < tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 5e-2)])
+@pytest.mark.parametrize("window", [None, 290, 130])
+@pytest.mark.parametrize("sizes", [(3, 40, 24, 40), (4, 16, 24, 64), (16, 16, 16, 128), (2, 32, 32, 256)])
+def test_latent_attention_decoded_tokens_alone(cuda_kernels, dtype, tol, window, sizes):
+    """A step of single tokens only: the tiled kernel cuts the keys over several blocks and merges."""
+    H, dk, dv, r = sizes
+    assert _attention_case(cuda_kernels, dtype, window, True, H=H, dk=dk, dv=dv, r=r, n=420, seed=30, decode_only=True) < tol
+
+
+def test_latent_attention_tiles_against_the_per_token_kernel(cuda_kernels):
+    """The two bfloat16 paths on the same case."""
+    try:
+        tiles = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=4, dk=32, dv=48, r=96, n=300, seed=50)
+        cuda_kernels.latent_tiles = False
+        plain = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=4, dk=32, dv=48, r=96, n=300, seed=50)
+    finally:
+        cuda_kernels.latent_tiles = True
+    assert tiles < 5e-2 and plain < 5e-2
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 3e-2)])
@@ -249,13 +290,28 @@ def _runner(d, dtype, page, kernels, pages=None, **kw):
     return ModelRunner(model, kernels, page_size=page, num_pages=pages or 256 // page, max_seqs=4, max_seq_len=512, **kw)
 
 
+def _bf16_close(name, got, want, yard):
+    """bfloat16 logits against the exact ones.  The yardstick is the plain implementation run in bfloat16 arithmetic
+    on the same rounded weights: what rounding alone does to this model.  These models are made sharp (scores of 20
+    and more), so two correct bfloat16 computations that round at different places differ by about as much as either
+    differs from the exact result; the engine may be up to three times as far off as the yardstick in the worst row,
+    twice on average, and has to agree with the exact best token about as often."""
+    err, bound = np.abs(got - want).max(axis=1), np.abs(yard - want).max(axis=1)
+    assert float(err.max()) <= 3.0 * float(bound.max()), \
+        f"{name}: row {int(err.argmax())} is off by {float(err.max()):.4f}; rounding alone gives {float(bound.max()):.4f}"
+    assert float(err.mean()) <= 2.0 * float(bound.mean()), f"{name}: mean error {float(err.mean()):.4f} against {float(bound.mean()):.4f}"
+    agree = float(np.mean(got.argmax(-1) == want.argmax(-1)))
+    assert agree >= float(np.mean(yard.argmax(-1) == want.argmax(-1))) - 0.1, f"{name}: best token agrees at {agree:.2f}"
+
+
 def _check(name, dtype, got, o):
     if dtype == "float32":
-        bad = helpers.first_bad(got, o["float32"], 3e-4)
+        top = max(float(np.abs(v).max()) for v in o["float32"].values())
+        bad = helpers.first_bad(got, o["float32"], 2e-4 + 1e-5 * top)          # float32 rounding grows with the logits
         assert bad is None, f"{name}: first wrong row (request, position, diff): {bad}"
     else:
         for rid in o["reqs"]:
-            helpers.bf16_check(f"{name} {rid}", got[rid], o["bfloat16"][rid], o["yard"][rid])
+            _bf16_close(f"{name} {rid}", got[rid], o["bfloat16"][rid], o["yard"][rid])
 
 
 @pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
@@ -320,7 +376,7 @@ def test_long_decoding_with_pages_given_back_and_graphs(dtype, dafolorn_dirs, cu
         if dtype == "float32":
             assert float(np.abs(got[rid] - want[rid]).max()) < 3e-4, rid
         else:
-            helpers.bf16_check(rid, got[rid], want[rid], yard[rid])
+            _bf16_close(rid, got[rid], want[rid], yard[rid])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
