@@ -67,8 +67,9 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(   // 32 .. 1
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [rows of the block][stride]
   __nv_bfloat16* c_s = q_s + rows_blk * stride;                        // [2][32][stride]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int4 item = items[blockIdx.x / subs];
-  const int sub = blockIdx.x % subs;
+  const int bx = gridDim.x - 1 - blockIdx.x;                            // later tokens see more keys: they start first
+  const int4 item = items[bx / subs];
+  const int sub = bx % subs;
   const int tok0 = sub * QT;
   if (tok0 >= item.z) return;
   const int ntok = min(QT, item.z - tok0);
@@ -222,9 +223,11 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(   // 32 .. 1
       sum[e] += __shfl_xor_sync(0xffffffffu, sum[e], 2);
       l_run[e] = l_run[e] * corr[e] + sum[e];
     }
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {   // no row's maximum moved: nothing to rescale
 #pragma unroll
-    for (int i = 0; i < NT; ++i) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      for (int i = 0; i < NT; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
     }
     // O += P C: the weights as the product's A operand, the same latent tile transposed as B
 #pragma unroll

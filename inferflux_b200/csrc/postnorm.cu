@@ -118,6 +118,66 @@ __global__ void __launch_bounds__(1024) postnorm_add_rmsnorm_kernel(
   for (int i = threadIdx.x + PRE * blockDim.x; i < hidden; i += blockDim.x) conv_one(i, w_next[i]);
 }
 
+// Many rows: the same three passes with four elements per thread and step (16-byte loads of x, the weights and the
+// row buffer, 8 or 16 of y), for widths that are multiples of 4.  No convolution here: that is for steps of single tokens.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256) postnorm_add_rmsnorm_rows_kernel(
+    float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ w_post, float eps_post,
+    const float* __restrict__ w_next, float eps_next, TO* __restrict__ out, int hidden, int splits,
+    size_t split_stride) {
+  extern __shared__ __align__(16) float row_s[];
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  float* xr = x + row * hidden;
+  const TY* yr = y + row * hidden;
+  const int step = blockDim.x * 4;
+  float ss = 0.0f;
+  for (int i = threadIdx.x * 4; i < hidden; i += step) {
+    float4 v = ld4(yr + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 p = ld4(yr + (size_t)s * split_stride + i);
+      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    }
+    st4(row_s + i, v);
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float r1 = rsqrtf(ss / (float)hidden + eps_post);
+  float ss2 = 0.0f;
+  for (int i = threadIdx.x * 4; i < hidden; i += step) {
+    const float4 xv = ld4(xr + i), wv = ld4(w_post + i), yv = ld4(row_s + i);
+    const float4 v = make_float4(xv.x + yv.x * r1 * wv.x, xv.y + yv.y * r1 * wv.y, xv.z + yv.z * r1 * wv.z,
+                                 xv.w + yv.w * r1 * wv.w);
+    st4(xr + i, v);
+    st4(row_s + i, v);
+    ss2 = fmaf(v.x, v.x, ss2); ss2 = fmaf(v.y, v.y, ss2); ss2 = fmaf(v.z, v.z, ss2); ss2 = fmaf(v.w, v.w, ss2);
+  }
+  if (out == nullptr) return;
+  ss2 = block_sum(ss2, scratch);
+  const float r2 = rsqrtf(ss2 / (float)hidden + eps_next);
+  TO* o = out + row * hidden;
+  for (int i = threadIdx.x * 4; i < hidden; i += step) {
+    const float4 v = ld4(row_s + i), wv = ld4(w_next + i);
+    st4(o + i, make_float4(v.x * r2 * wv.x, v.y * r2 * wv.y, v.z * r2 * wv.z, v.w * r2 * wv.w));
+  }
+}
+
 template <typename T>
 __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
                                    long long rows, int hidden) {
@@ -144,6 +204,12 @@ __global__ void xielu_kernel(const TI* __restrict__ z, TO* __restrict__ out, lon
   }
 }
 
+// e^z - 1 through the fast exponential: its error of a few 1e-7 is far below what rounding the result to bfloat16 does
+// (the result is dominated by z / 2 where e^z - 1 - z is small).
+__device__ __forceinline__ float xielu_fast(float z, float a_pos, float a_neg) {
+  return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, (__expf(z) - 1.0f) - z, 0.5f * z);
+}
+
 // The same, eight bfloat16 (16 bytes) per thread and step, for element counts that are multiples of 8.
 __global__ void xielu_bf16x8_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ out, long long n8,
                                     float a_pos, float a_neg) {
@@ -153,7 +219,7 @@ __global__ void xielu_bf16x8_kernel(const __nv_bfloat16* __restrict__ z, __nv_bf
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 f = __bfloat1622float2(h2[k]);
-      h2[k] = __floats2bfloat162_rn(xielu_f(f.x, a_pos, a_neg), xielu_f(f.y, a_pos, a_neg));
+      h2[k] = __floats2bfloat162_rn(xielu_fast(f.x, a_pos, a_neg), xielu_fast(f.y, a_pos, a_neg));
     }
     reinterpret_cast<uint4*>(out)[i] = raw;
   }
@@ -192,14 +258,27 @@ int ifx_postnorm_add_rmsnorm(float* x, const void* y, const float* w_post, float
   const size_t split_stride = (size_t)T * hidden;
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return IFX_E_TOOBIG;
-  const int threads = (T <= 512 && hidden > 512) ? 1024 : 256;           // few rows: more threads a row
+  // A float32 run (float32 in, float32 out, no slices) always takes the same kernel with the same block, so that a
+  // row's sums are added in an order that depends on the width alone, never on how many rows share the launch.
+  const bool exact = y_dtype == IFX_DT_F32 && splits == 1 && (out == nullptr || out_dtype == IFX_DT_F32);
+  const int threads = (!exact && T <= 512 && hidden > 512) ? 1024 : 256;  // few rows: more threads a row
+  const bool rows_path = !exact && T > 512 && conv_w == nullptr && hidden % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+                         (uintptr_t)y % 16 == 0 && (out == nullptr || (uintptr_t)out % 16 == 0) &&
+                         (uintptr_t)w_post % 16 == 0 && (w_next == nullptr || (uintptr_t)w_next % 16 == 0);
   if (out != nullptr && w_next == nullptr) return IFX_E_BADARG;
 #define IFX_LAUNCH(TY, TO)                                                                                         \
   do {                                                                                                             \
-    auto kern = postnorm_add_rmsnorm_kernel<TY, TO>;                                                               \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    kern<<<T, threads, smem, stream>>>(x, (const TY*)y, w_post, eps_post, w_next, eps_next, (TO*)out, hidden, splits,  \
-                                   split_stride, conv);                                                            \
+    if (rows_path) {                                                                                               \
+      auto kern = postnorm_add_rmsnorm_rows_kernel<TY, TO>;                                                        \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+      kern<<<T, 256, smem, stream>>>(x, (const TY*)y, w_post, eps_post, w_next, eps_next, (TO*)out, hidden, splits, \
+                                     split_stride);                                                                \
+    } else {                                                                                                       \
+      auto kern = postnorm_add_rmsnorm_kernel<TY, TO>;                                                             \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+      kern<<<T, threads, smem, stream>>>(x, (const TY*)y, w_post, eps_post, w_next, eps_next, (TO*)out, hidden,    \
+                                         splits, split_stride, conv);                                              \
+    }                                                                                                              \
   } while (0)
   const int od = out == nullptr ? IFX_DT_F32 : out_dtype;
   if (y_dtype == IFX_DT_F32 && od == IFX_DT_F32) IFX_LAUNCH(float, float);
