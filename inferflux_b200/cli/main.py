@@ -109,7 +109,7 @@ def cmd_status(_args) -> int:
     from ..config import registered_architectures
     from ..parts import registered_parts
     info = {"cuda": torch.cuda.is_available(), "architectures": registered_architectures(),
-            "parts": {role: registered_parts(role) for role in ("mixer", "ffn", "norm", "position", "block")}}
+            "parts": {role: registered_parts(role) for role in ("mixer", "ffn", "norm", "position", "conv", "merge", "block")}}
     if torch.cuda.is_available():
         info["device"] = torch.cuda.get_device_name(0)
         from ..csrc import build
@@ -135,7 +135,7 @@ def cmd_info(args) -> int:
             cmd_models(args)
         out["model"] = json.loads(buf.getvalue())
         specs = Model(load_config(args.model).to_plan()).cache_specs()
-        out["model"]["kv_bytes_per_token_bf16"] = sum(2 * kv.num_kv_heads * kv.head_dim * 2 for kv, _st in specs if kv)
+        out["model"]["kv_bytes_per_token_bf16"] = sum(kv.planes * kv.num_kv_heads * kv.head_dim * 2 for kv, _st in specs if kv)
     print(json.dumps(out, indent=2))
     return 0
 

@@ -56,7 +56,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // items[i] = (slot, first flat token, tokens, first position): up to 64 consecutive tokens of one request.
 // Block (x, y, z): item x / subs, its tokens [sub * QT, (sub + 1) * QT) with sub = x % subs; heads y * HC ..; key part z.
 template <int RMAX>
-__global__ void __launch_bounds__(128) latent_attention_mma_kernel(   // 32 .. 128 threads: a warp per 16 rows
+__global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .. 128 threads: a warp per 16 rows; three blocks a SM
     const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table,
     const int4* __restrict__ items, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float2* __restrict__ part_ml, int total_rows, int heads, int rank, int page_size,

@@ -862,10 +862,17 @@ class CudaKernels:
         ql = self.linear_heads(q_rows, w_uk, heads, dim, rank, w_is_nk=False)               # [T, heads * rank]
         win = 0 if window is None else int(window)
         splits = 1
+        max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
         if ctx.max_span == 1:                              # decoded tokens only: cut the keys so that the SMs fill
-            max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
             blocks = num_items * -(-heads // 64)                 # about four warps a SM, at least two key tiles each
             splits = max(1, min(592 // max(1, blocks), max_keys // 64, 64))
+        else:
+            # prompt portions: a block walks its keys tile after tile, and the last tokens' blocks walk all of them;
+            # while the grid does not fill the SMs twice over (three blocks a SM), cut every block's keys in 2..4
+            hc = min(heads, 64)
+            qt = max(1, min(64 // hc, self.LATENT_TILE, ctx.max_span))
+            blocks = -(-T // qt) * -(-heads // 64)
+            splits = max(1, min(888 // max(1, blocks), max_keys // 256, 4))
         ws = None
         if splits > 1:
             ws = torch.empty(int(self.lib.ifx_latent_attention_mma_workspace(T * heads, rank, splits)), dtype=torch.uint8,

@@ -57,9 +57,10 @@ __global__ void short_conv_kernel(const T* __restrict__ h, const float* __restri
 }
 
 // The same for up to 4 taps and channel counts that are multiples of 16 bytes' worth of elements: a thread owns
-// VEC consecutive channels (one 16-byte load per input row) and walks kConvRows consecutive tokens, so that the
-// chain of metadata loads (token -> request -> span and slot) is paid once per request a block meets, not per element.
-constexpr int kConvRows = 4;
+// VEC consecutive channels (one 16-byte load per input row) and, in steps of many tokens, walks up to kConvRows
+// consecutive tokens, so that the chain of metadata loads (token -> request -> span and slot) is paid once per
+// request a block meets and a token's earlier inputs stay in registers for the next token.
+constexpr int kConvRows = 8;
 
 template <typename T> struct ConvVec;
 template <> struct ConvVec<float> {
@@ -96,7 +97,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) short_conv_vec_kernel(
     const T* __restrict__ h, const float* __restrict__ w, float* __restrict__ state, long long state_slot_stride,
     const int* __restrict__ token_req, const int* __restrict__ req_slot, const int* __restrict__ cu_seqlens,
-    T* __restrict__ out, int num_tokens, int channels, int taps, int inline_single) {
+    T* __restrict__ out, int num_tokens, int channels, int taps, int inline_single, int rows_per_block) {
   constexpr int V = ConvVec<T>::N;
   const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
   if (c0 >= channels) return;
@@ -105,23 +106,30 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
   for (int v = 0; v < V; ++v)
 #pragma unroll
     for (int k = 0; k < 4; ++k) wr[v][k] = k < taps ? w[(size_t)(c0 + v) * taps + (taps - 1 - k)] : 0.0f;
-  const int t_end = min(num_tokens, (int)(blockIdx.x + 1) * kConvRows);
+  const int t_end = min(num_tokens, (int)(blockIdx.x + 1) * rows_per_block);
   int r_at = -1, first = 0, n = 0;
   float* st = nullptr;
-  for (int t = blockIdx.x * kConvRows; t < t_end; ++t) {
+  float in[4][V];                                        // in[k]: the input k steps back
+  for (int t = blockIdx.x * rows_per_block; t < t_end; ++t) {
     const int r = token_req[t];
-    if (r != r_at) {
+    const bool carry = r == r_at;                        // the token before is this request's too: its inputs are in registers
+    if (!carry) {
       r_at = r;
       first = cu_seqlens[r];
       n = cu_seqlens[r + 1] - first;
       st = state ? state + (long long)req_slot[r] * state_slot_stride : nullptr;
     }
     const int i = t - first;
-    float in[4][V];                                      // in[k]: the input k steps back
+    if (carry) {
+#pragma unroll
+      for (int k = 3; k >= 1; --k)
+#pragma unroll
+        for (int v = 0; v < V; ++v) in[k][v] = in[k - 1][v];
+    }
     ConvVec<T>::load(h + (size_t)t * channels + c0, in[0]);
 #pragma unroll
     for (int k = 1; k < 4; ++k) {
-      if (k < taps) {
+      if (k < taps && !carry) {
         if (k <= i) {
           ConvVec<T>::load(h + (size_t)(t - k) * channels + c0, in[k]);
         } else {
@@ -205,13 +213,14 @@ int ifx_short_conv(const void* h, const float* w, float* state, long long state_
   const bool wide = taps <= 4 && channels % vec == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
                     (state == nullptr || ((uintptr_t)state % 16 == 0 && state_slot_stride % 4 == 0));
   const int vthreads = channels / vec >= 256 ? 256 : ((channels / vec + 31) / 32) * 32;
-  dim3 vgrid((unsigned)((T + kConvRows - 1) / kConvRows), wide ? (unsigned)((channels / vec + vthreads - 1) / vthreads) : 1u);
+  const int rows_per_block = T >= 256 * kConvRows ? kConvRows : (T >= 256 ? T / 256 : 1);
+  dim3 vgrid((unsigned)((T + rows_per_block - 1) / rows_per_block), wide ? (unsigned)((channels / vec + vthreads - 1) / vthreads) : 1u);
 #define IFX_LAUNCH(TT)                                                                                              \
   do {                                                                                                              \
     if (wide)                                                                                                       \
       short_conv_vec_kernel<TT><<<vgrid, vthreads, 0, stream>>>((const TT*)h, w, state, state_slot_stride,          \
                                                                 token_req, req_slot, cu_seqlens, (TT*)out, T,       \
-                                                                channels, taps, 1);                                 \
+                                                                channels, taps, 1, rows_per_block);                 \
     else                                                                                                            \
       short_conv_kernel<TT><<<grid, threads, 0, stream>>>((const TT*)h, w, state, state_slot_stride, token_req,     \
                                                            req_slot, cu_seqlens, (TT*)out, channels, taps, 1);      \

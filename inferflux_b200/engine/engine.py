@@ -118,9 +118,10 @@ class Engine:
     # ------------------------------------------------------------------ sizing
     def bytes_per_token(self) -> int:
         """Cache bytes one token takes over all caches (2 . layers . kv_heads . head_dim . itemsize
-        for a plain decoder, runtime/backends/cuda/native/kv_cache_planner.h:22-37)."""
+        for a plain decoder, runtime/backends/cuda/native/kv_cache_planner.h:22-37; one plane instead of two
+        where a mixer caches a single latent)."""
         item = torch.empty(0, dtype=self.dtype).element_size()
-        return sum(2 * kv.num_kv_heads * kv.head_dim * item for kv, _st in self.model.cache_specs() if kv)
+        return sum(kv.planes * kv.num_kv_heads * kv.head_dim * item for kv, _st in self.model.cache_specs() if kv)
 
     def state_bytes_per_request(self) -> int:
         """Bytes of fixed-size state one request slot takes over all caches."""

@@ -167,7 +167,7 @@ def _attention_case(kernels, dtype, window, sink, H=3, dk=40, dv=24, r=40, n=420
     c = c.to(dtype).double()                                              # what the cache holds
     scale = 1.7 / math.sqrt(dk)
     cache = CacheManager([(KVCacheSpec(1, r, window, planes=1), None)], page_size=page, num_pages=3 * (n // page + 1),
-                         max_seqs=4, max_seq_len=512, dtype=dtype, device=DEV)
+                         max_seqs=4, max_seq_len=max(512, n + 16), dtype=dtype, device=DEV)
     view = lambda: cache.view(ScheduleEntry(0, 0))
     spans = [(rid, head) for rid, (head, _e) in spans_of.items()]         # first the prefixes, in one step
     ctx, starts = _step_ctx(kernels, dtype, cache, spans)
@@ -219,6 +219,16 @@ def test_latent_attention_decoded_tokens_alone(cuda_kernels, dtype, tol, window,
     """A step of single tokens only: the tiled kernel cuts the keys over several blocks and merges."""
     H, dk, dv, r = sizes
     assert _attention_case(cuda_kernels, dtype, window, True, H=H, dk=dk, dv=dv, r=r, n=420, seed=30, decode_only=True) < tol
+
+
+@pytest.mark.parametrize("window", [None, 600, 300])
+@pytest.mark.parametrize("sizes", [(4, 16, 24, 64), (12, 8, 8, 128), (3, 40, 24, 40)])
+def test_latent_attention_prompt_portions_over_many_keys(cuda_kernels, window, sizes):
+    """Portions behind 1,000 cached tokens: with few blocks and many keys the tiled kernel cuts the keys of
+    prompt portions too, and merges."""
+    H, dk, dv, r = sizes
+    assert _attention_case(cuda_kernels, torch.bfloat16, window, True, H=H, dk=dk, dv=dv, r=r, n=1100, seed=70) < 5e-2
+    assert _attention_case(cuda_kernels, torch.float32, window, True, H=H, dk=dk, dv=dv, r=r, n=1100, seed=70) < 2e-5
 
 
 def test_latent_attention_tiles_against_the_per_token_kernel(cuda_kernels):
