@@ -42,6 +42,7 @@ constexpr int kTileN = 128;       // weight rows per block (MMA M)
 constexpr int kTileK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
 
 enum { MODE_STORE = 0, MODE_PARTIAL = 1, MODE_SWIGLU = 2, MODE_SWIGLU64 = 3 };
+enum { ACT_NONE = 0, ACT_XIELU = 1 };                  // an activation on the stored result of MODE_STORE
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
   // K-major tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -73,7 +74,8 @@ __global__ void __launch_bounds__(192)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                    const float* __restrict__ bias, void* __restrict__ out, float* __restrict__ partials, int M, int N,
                    int K, int kblocks_per_split, int up_row_offset, int out_is_f32, int stages,
-                   const float* __restrict__ row_sumsq, int sumsq_chunks, float eps, int* __restrict__ error_flag) {
+                   const float* __restrict__ row_sumsq, int sumsq_chunks, float eps, int* __restrict__ error_flag,
+                   int act_kind, float act_a, float act_b) {
   constexpr int W_TILES = MODE == MODE_SWIGLU ? 2 : 1;
   constexpr uint32_t W_BYTES = kTileN * kTileK * 2;                 // 16 KB
   constexpr uint32_t A_BYTES = NPAD * kTileK * 2;
@@ -253,10 +255,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           }
           if (MODE == MODE_PARTIAL) {
             partials[((size_t)split * M + m) * N + n] = v;
-          } else if (out_is_f32) {
-            reinterpret_cast<float*>(out)[(size_t)m * N + n] = v + b;
           } else {
-            reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v + b);
+            float r = v + b;
+            if (MODE == MODE_STORE && act_kind == ACT_XIELU)     // a z^2 + z/2 above zero, b (e^z - 1 - z) + z/2 below
+              r = r > 0.0f ? fmaf(act_a * r, r, 0.5f * r) : fmaf(act_b, (__expf(r) - 1.0f) - r, 0.5f * r);
+            if (out_is_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = r;
+            else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(r);
           }
         }
       }
@@ -319,7 +323,8 @@ static size_t skinny_smem_bytes(int npad, int mode, int stages) {
 template <int NPAD, int MODE>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, float* partials,
                          int M, int N, int K, int splits, int up_row_offset, int out_is_f32, const float* row_sumsq,
-                         int sumsq_chunks, float eps, int* error_flag, cudaStream_t stream) {
+                         int sumsq_chunks, float eps, int* error_flag, cudaStream_t stream, int act_kind, float act_a,
+                         float act_b) {
   const int total_kblocks = (K + kTileK - 1) / kTileK;
   const int per_split = (total_kblocks + splits - 1) / splits;
   // As many stages as fit the block's share of shared memory, at most the k-blocks of a split.  A grid of at most
@@ -341,7 +346,8 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
     configured = smem;
   }
   return launch_pdl(gemm_skinny_kernel<NPAD, MODE>, grid, dim3(192), smem, stream, 1, mw, ma, bias, out, partials, M, N,
-                    K, per_split, up_row_offset, out_is_f32, stages, row_sumsq, sumsq_chunks, eps, error_flag);
+                    K, per_split, up_row_offset, out_is_f32, stages, row_sumsq, sumsq_chunks, eps, error_flag, act_kind,
+                    act_a, act_b);
 }
 
 }  // namespace ifx
@@ -355,11 +361,12 @@ using namespace ifx;
 // error_flag: device int, set to non-zero if a bounded wait ran out (the output is then not valid).
 // row_sumsq (optional): float32 [M, sumsq_chunks]; the rows of `act` are then x * w of a norm over K
 // columns and every output row m is scaled by rsqrt(sum(row_sumsq[m, :]) / K + eps).
-extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias, void* out, float* partials, int M,
-                               int N, int K, int w_rows, int splits, int mode, int up_row_offset, int out_is_f32,
-                               const float* row_sumsq, int sumsq_chunks, float eps, int* error_flag,
-                               cudaStream_t stream) {
+static int gemm_skinny_any(const void* act, const void* W, const float* bias, void* out, float* partials, int M,
+                          int N, int K, int w_rows, int splits, int mode, int up_row_offset, int out_is_f32,
+                          const float* row_sumsq, int sumsq_chunks, float eps, int* error_flag, cudaStream_t stream,
+                          int act_kind, float act_a, float act_b) {
   if (M <= 0 || N <= 0) return 0;
+  if (act_kind != ACT_NONE && (act_kind != ACT_XIELU || mode != MODE_STORE)) return IFX_E_BADARG;
   if (K <= 0 || M > 256 || splits <= 0 || splits > 65535 || error_flag == nullptr) return IFX_E_BADARG;
   if (mode == MODE_STORE && splits != 1) return IFX_E_BADARG;
   if (mode == MODE_SWIGLU && (splits != 1 || out_is_f32)) return IFX_E_BADARG;
@@ -376,7 +383,7 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   if (rc) return rc;
 #define LAUNCH(NP, MD) \
   return launch_skinny<NP, MD>(mw, ma, bias, out, partials, M, N, K, splits, up_row_offset, out_is_f32, row_sumsq, \
-                               sumsq_chunks, eps, error_flag, stream)
+                               sumsq_chunks, eps, error_flag, stream, act_kind, act_a, act_b)
 #define BY_NPAD(MD)                 \
   switch (npad) {                   \
     case 16: LAUNCH(16, MD);        \
@@ -390,4 +397,21 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   if (mode == MODE_SWIGLU) { BY_NPAD(MODE_SWIGLU) }
   if (mode == MODE_SWIGLU64) { BY_NPAD(MODE_SWIGLU64) }
   return IFX_E_BADARG;
+}
+
+extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias, void* out, float* partials, int M,
+                               int N, int K, int w_rows, int splits, int mode, int up_row_offset, int out_is_f32,
+                               const float* row_sumsq, int sumsq_chunks, float eps, int* error_flag,
+                               cudaStream_t stream) {
+  return gemm_skinny_any(act, W, bias, out, partials, M, N, K, w_rows, splits, mode, up_row_offset, out_is_f32, row_sumsq,
+                         sumsq_chunks, eps, error_flag, stream, ACT_NONE, 0.0f, 0.0f);
+}
+
+// mode 0 with an activation on the result before it is stored: act_kind 1 = xIELU with its two factors
+// (act_a z^2 + z/2 for z > 0, act_b (e^z - 1 - z) + z/2 otherwise).
+extern "C" int ifx_gemm_skinny_act(const void* act, const void* W, const float* bias, void* out, int M, int N, int K,
+                                   int w_rows, int out_is_f32, const float* row_sumsq, int sumsq_chunks, float eps,
+                                   int act_kind, float act_a, float act_b, int* error_flag, cudaStream_t stream) {
+  return gemm_skinny_any(act, W, bias, out, nullptr, M, N, K, w_rows, 1, MODE_STORE, 0, out_is_f32, row_sumsq,
+                         sumsq_chunks, eps, error_flag, stream, act_kind, act_a, act_b);
 }

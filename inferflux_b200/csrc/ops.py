@@ -143,7 +143,7 @@ class CudaKernels:
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows",
                    "ifx_gemm_tcgen05", "ifx_postnorm_add_rmsnorm", "ifx_concat_cast", "ifx_xielu", "ifx_softcap",
                    "ifx_short_conv", "ifx_latent_norm_append", "ifx_latent_attention_generic", "ifx_latent_attention_mma",
-                   "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched"):
+                   "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched", "ifx_gemm_skinny_act"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
@@ -376,6 +376,23 @@ class CudaKernels:
                 and a.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0 and a.is_contiguous()):
             return self.linear_tiles(a, w_gate_up, swiglu=True)        # many rows: own tcgen05 tiles, activation fused
         return self.silu_mul(self.linear(a, w_gate_up))
+
+    def linear_xielu(self, a, w, a_pos, a_neg):
+        """xielu(a . w^T): for few bfloat16 rows and a product wide enough to fill the SMs without K slices, the
+        weight-streaming kernel with the activation on its result; otherwise the product (maybe in K slices)
+        followed by the activation kernel, which adds the slices."""
+        T, K = a.shape
+        N = w.shape[0]
+        if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < T <= self.SKINNY_MAX_ROWS and K % 8 == 0
+                and a.is_contiguous() and w.is_contiguous() and w.shape[1] == K and a.data_ptr() % 16 == 0
+                and w.data_ptr() % 16 == 0 and -(-N // 128) >= 74):
+            out = torch.empty((T, N), dtype=torch.bfloat16, device=a.device)
+            _check(self.lib.ifx_gemm_skinny_act(_ptr(a), _ptr(w), _ptr(None), _ptr(out), T, N, K, w.shape[0], 0, _ptr(None), 0,
+                                                ctypes.c_float(0.0), 1, ctypes.c_float(a_pos), ctypes.c_float(a_neg),
+                                                _ptr(self.error_flag), _stream()), "gemm_skinny (xielu)")
+            self.launches += 1
+            return out
+        return self.xielu(self.linear(a, w, allow_partial=True), a_pos, a_neg)
 
     def check_errors(self):
         """Raise if a kernel reported that one of its bounded waits ran out (reads the device flag)."""

@@ -48,6 +48,23 @@ __global__ void __launch_bounds__(1024) postnorm_add_rmsnorm_kernel(
     wp_pre[j] = i < hidden ? w_post[i] : 0.0f;
     wn_pre[j] = (i < hidden && out != nullptr) ? w_next[i] : 0.0f;
   }
+  // the convolution's taps and the request's state do not depend on a reduction either (up to 4 taps: 3 cells)
+  const bool conv_pre = conv.w != nullptr && conv.taps <= 4;
+  float* st_pre = nullptr;
+  float old_pre[PRE][3], tap_pre[PRE][4];
+  if (conv_pre) {
+    st_pre = conv.taps > 1 ? conv.state + (long long)conv.req_slot[conv.token_req[row]] * conv.slot_stride : nullptr;
+#pragma unroll
+    for (int j = 0; j < PRE; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+#pragma unroll
+      for (int k = 0; k < 3; ++k)                          // old_pre[j][k]: the input k + 1 steps back
+        old_pre[j][k] = (i < hidden && k < conv.taps - 1) ? st_pre[(size_t)(conv.taps - 2 - k) * hidden + i] : 0.0f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)                          // tap_pre[j][k]: the tap of the input k steps back
+        tap_pre[j][k] = (i < hidden && k < conv.taps) ? conv.w[(size_t)i * conv.taps + conv.taps - 1 - k] : 0.0f;
+    }
+  }
   float ss = 0.0f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = to_f32(yr[i]);
@@ -113,7 +130,21 @@ __global__ void __launch_bounds__(1024) postnorm_add_rmsnorm_kernel(
 #pragma unroll
   for (int j = 0; j < PRE; ++j) {
     const int i = threadIdx.x + j * blockDim.x;
-    if (i < hidden) conv_one(i, wn_pre[j]);
+    if (i >= hidden) continue;
+    if (!conv_pre) {
+      conv_one(i, wn_pre[j]);
+      continue;
+    }
+    // the same sums in the same order, from what was fetched at the start
+    const float h = to_f32(from_f32<TO>(row_s[i] * r2 * wn_pre[j]));
+    float acc = fmaf(tap_pre[j][0], h, h);
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      if (k < taps - 1) {
+        acc = fmaf(tap_pre[j][k + 1], old_pre[j][k], acc);
+        st_pre[(size_t)(taps - 2 - k) * hidden + i] = k == 0 ? h : old_pre[j][k - 1 < 0 ? 0 : k - 1];
+      }
+    o[i] = from_f32<TO>(acc);
   }
   for (int i = threadIdx.x + PRE * blockDim.x; i < hidden; i += blockDim.x) conv_one(i, w_next[i]);
 }

@@ -89,5 +89,5 @@ class ActivationMLP(FeedForward):
 
     def forward(self, h, ctx):
         k = ctx.kernels
-        z = k.linear(h, self.w_up, allow_partial=True)            # maybe in K slices: the activation kernel adds them
-        return k.linear(k.xielu(z, self.a_pos, self.a_neg), self.w_down, allow_partial=True)
+        act = k.linear_xielu(h, self.w_up, self.a_pos, self.a_neg)     # the activation in the product's epilogue where it can be
+        return k.linear(act, self.w_down, allow_partial=True)

@@ -137,6 +137,9 @@ class PlainKernels:
         neg = a_neg * (torch.expm1(torch.clamp(za, max=0.0)) - za) + 0.5 * za
         return torch.where(za > 0, a_pos * za * za + 0.5 * za, neg).to(z.dtype)
 
+    def linear_xielu(self, a, w, a_pos, a_neg):
+        return self.xielu(self.linear(a, w), a_pos, a_neg)
+
     def softcap(self, logits, cap):
         logits.copy_(cap * torch.tanh(logits.to(self.acc) / cap))
 

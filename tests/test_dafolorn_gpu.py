@@ -103,6 +103,22 @@ def test_xielu_softcap_concat(cuda_kernels, dtype, tol):
     assert torch.equal(both, torch.cat([a, b], dim=1).to(dtype))
 
 
+@pytest.mark.parametrize("T,N,K", [(8, 9600, 256), (37, 9472, 136), (8, 640, 256), (200, 9600, 64)])
+def test_product_with_the_activation_in_its_epilogue(cuda_kernels, T, N, K):
+    """Wide products of few rows apply xIELU before they store (one kernel); the others take the product and
+    the activation kernel.  Both against the plain functions."""
+    a, w = _rnd(T, K, seed=1).to(torch.bfloat16), _rnd(N, K, seed=2, scale=0.2).to(torch.bfloat16)
+    p, q = 0.2, -0.4
+    sp = lambda v: math.log1p(math.exp(v))
+    before = cuda_kernels.launches + cuda_kernels.library_calls
+    got = cuda_kernels.linear_xielu(a.to(DEV), w.to(DEV), sp(p), 0.5 + sp(q)).cpu().double()
+    cuda_kernels.check_errors()
+    assert (cuda_kernels.launches + cuda_kernels.library_calls - before == 1) == (T <= 160 and N >= 74 * 128 - 127)
+    want = P.xielu(a.double() @ w.double().T, p, q)
+    # the unfused path rounds the product to bfloat16 before the activation squares it: two roundings and a doubling
+    assert float(((got - want).abs() / (1 + want.abs())).max()) < 2e-2
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
 def test_short_conv_over_steps_and_requests(cuda_kernels, dtype, tol, taps):
@@ -181,7 +197,7 @@ def _attention_case(kernels, dtype, window, sink, H=3, dk=40, dv=24, r=40, n=420
                                    H, dk, dv, r, window, scale, ctx, view()).cpu().double()
     _commit(cache, spans, starts)
     kernels.check_errors()
-    worst, row = 0.0, 0
+    worst, yard, row = 0.0, 0.0, 0
     for rid, (head, end) in spans_of.items():
         for i in range(head, end):
             lo = max(0, i - W + 1)
@@ -191,20 +207,28 @@ def _attention_case(kernels, dtype, window, sink, H=3, dk=40, dv=24, r=40, n=420
                 p = P.windowed_sink_softmax(s, sinks[a].double() if sink else -1e30)
                 want = w_uv.double()[a * dv:(a + 1) * dv] @ (p @ c[lo:i + 1])
                 worst = max(worst, float((got[row, a * dv:(a + 1) * dv] - want).abs().max()) / (1e-3 + float(want.abs().max())))
+                if dtype == torch.bfloat16:      # the yardstick: the same sums with the three roundings any bfloat16 path through latent space has
+                    rb = lambda t: t.to(torch.bfloat16).double()
+                    s2 = (c[lo:i + 1] @ rb(w_uk.double()[a * dk:(a + 1) * dk].T @ q)) * scale
+                    p2 = P.windowed_sink_softmax(s2, sinks[a].double() if sink else -1e30)
+                    rough = w_uv.double()[a * dv:(a + 1) * dv] @ rb(rb(p2) @ c[lo:i + 1])
+                    yard = max(yard, float((rough - want).abs().max()) / (1e-3 + float(want.abs().max())))
             row += 1
-    return worst
+    # bfloat16: up to three times what those roundings alone do to this case (its planted scores are 20 and more)
+    return worst if dtype == torch.float32 else worst / max(1.0, 3.0 * yard / 2e-2)
 
 
 # bfloat16 takes the tensor-core tiles for latents that are multiples of 16 (up to 256), else the per-token kernel
-# (bfloat16: the planted keys have scores of 20 and more, so that rounding a query or a latent moves a weight by percents)
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 5e-2)])
+# (bfloat16: the planted keys have scores of 20 and more, so that rounding a query or a latent moves a weight by percents;
+# _attention_case scales its result by what the unavoidable roundings do to the case, so the bound stays 2e-2)
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("window,sink", [(37, True), (16, True), (17, False), (1, True), (None, True), (300, False)])
 @pytest.mark.parametrize("r", [40, 64])
 def test_latent_attention_kernels_planted_keys(cuda_kernels, dtype, tol, window, sink, r):
     assert _attention_case(cuda_kernels, dtype, window, sink, r=r) < tol
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 5e-2)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("sizes", [(1, 8, 8, 24), (5, 16, 40, 72), (2, 64, 64, 128), (4, 24, 16, 200), (2, 128, 128, 512),
                                    (6, 24, 40, 48), (16, 32, 32, 256), (70, 8, 8, 32), (3, 16, 16, 16), (64, 8, 16, 80)])
 def test_latent_attention_kernels_other_sizes(cuda_kernels, dtype, tol, sizes):
@@ -212,7 +236,7 @@ def test_latent_attention_kernels_other_sizes(cuda_kernels, dtype, tol, sizes):
     assert _attention_case(cuda_kernels, dtype, 45, True, H=H, dk=dk, dv=dv, r=r, n=140, seed=20) < tol
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 5e-2)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("window", [None, 290, 130])
 @pytest.mark.parametrize("sizes", [(3, 40, 24, 40), (4, 16, 24, 64), (16, 16, 16, 128), (2, 32, 32, 256)])
 def test_latent_attention_decoded_tokens_alone(cuda_kernels, dtype, tol, window, sizes):
@@ -227,7 +251,7 @@ def test_latent_attention_prompt_portions_over_many_keys(cuda_kernels, window, s
     """Portions behind 1,000 cached tokens: with few blocks and many keys the tiled kernel cuts the keys of
     prompt portions too, and merges."""
     H, dk, dv, r = sizes
-    assert _attention_case(cuda_kernels, torch.bfloat16, window, True, H=H, dk=dk, dv=dv, r=r, n=1100, seed=70) < 5e-2
+    assert _attention_case(cuda_kernels, torch.bfloat16, window, True, H=H, dk=dk, dv=dv, r=r, n=1100, seed=70) < 2e-2
     assert _attention_case(cuda_kernels, torch.float32, window, True, H=H, dk=dk, dv=dv, r=r, n=1100, seed=70) < 2e-5
 
 
@@ -239,7 +263,7 @@ def test_latent_attention_tiles_against_the_per_token_kernel(cuda_kernels):
         plain = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=4, dk=32, dv=48, r=96, n=300, seed=50)
     finally:
         cuda_kernels.latent_tiles = True
-    assert tiles < 5e-2 and plain < 5e-2
+    assert tiles < 2e-2 and plain < 2e-2
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 3e-2)])
