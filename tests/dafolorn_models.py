@@ -21,7 +21,7 @@ def _layer(heads, dim, vdim, rank, window, ff, scale=None):
 def configs():
     """name -> (config.json as a dict, page size).  Between them: one head and several; key size above,
     below and equal to the value size; latents that are no multiple of 32; windows of 1, below a page,
-    exactly a page, a page + 1, above the prompt lengths, and none; a layer without feed-forward; 1 to 4
+    exactly a page, a page + 1, above the prompt lengths, and none; a layer without feed-forward; 1 to 6
     taps and no convolution at all; a loop at the start, in the middle, over everything, run once, and
     none; with and without a cap on the logits."""
     p = {"architecture": "Dafolorn", "vocab": 300, "width": 64, "norm": {"eps": 1e-6}, "canon": {"taps": 3},
@@ -38,7 +38,10 @@ def configs():
     u = {"architecture": "Dafolorn", "vocab": 211, "width": 72, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
          "logit_softcap": 50.0, "loop": {"start": 1, "stop": 2, "times": 4},
          "layers": [_layer(3, 16, 8, 56, 9, 88), _layer(2, 16, 32, 24, 30, 104)]}
-    return {"P": (p, 8), "Q": (q, 16), "R": (r, 16), "S": (s, 4), "U": (u, 16)}
+    v = {"architecture": "Dafolorn", "vocab": 150, "width": 40, "norm": {"eps": 1e-6}, "canon": {"taps": 6},
+         "logit_softcap": 15.0, "loop": {"start": 0, "stop": 1, "times": 2},
+         "layers": [_layer(2, 16, 16, 32, 12, 48), _layer(1, 8, 24, 16, None, None)]}
+    return {"P": (p, 8), "Q": (q, 16), "R": (r, 16), "S": (s, 4), "U": (u, 16), "V": (v, 16)}
 
 
 def write_model(raw, out_dir, seed, sharpen=10.0):

@@ -193,7 +193,7 @@ def test_wrong_weights_are_refused(dafolorn_dirs, tmp_path):
 LENS = [40, 33, 50, 61, 97, 70, 25, 64, 1, 2]
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U", "V"])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_engine_host_logic_on_plain_kernels(name, cutting, dafolorn_dirs):
     from inferflux_b200.engine import ModelRunner

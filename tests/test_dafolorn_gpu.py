@@ -258,9 +258,9 @@ def test_latent_attention_prompt_portions_over_many_keys(cuda_kernels, window, s
 def test_latent_attention_tiles_against_the_per_token_kernel(cuda_kernels):
     """The two bfloat16 paths on the same case."""
     try:
-        tiles = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=4, dk=32, dv=48, r=96, n=300, seed=50)
+        tiles = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=5, dk=24, dv=40, r=96, n=300, seed=50)
         cuda_kernels.latent_tiles = False
-        plain = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=4, dk=32, dv=48, r=96, n=300, seed=50)
+        plain = _attention_case(cuda_kernels, torch.bfloat16, 70, True, H=5, dk=24, dv=40, r=96, n=300, seed=50)
     finally:
         cuda_kernels.latent_tiles = True
     assert tiles < 2e-2 and plain < 2e-2
@@ -348,7 +348,7 @@ def _check(name, dtype, got, o):
             _bf16_close(f"{name} {rid}", got[rid], o["bfloat16"][rid], o["yard"][rid])
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U", "V"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_step_function_cuttings(name, dtype, cutting, dafolorn_dirs, oracle, cuda_kernels):
