@@ -167,10 +167,11 @@ class CacheManager:
     # --------------------------------------------------------------------- pages
     def _first_needed_block(self, group: _Group, next_position: int) -> int:
         """Lowest block a query at `next_position` (and any later one) still reads."""
-        w = group.spec.window
-        if w is None:
-            return 0
-        return max(0, next_position - w + 1) // self.page_size
+        w, c = group.spec.window, group.spec.chunk
+        first = 0 if w is None else max(0, next_position - w + 1)
+        if c:
+            first = max(first, next_position // c * c)       # the stretch of positions that next_position lies in
+        return first // self.page_size
 
     def pages_needed(self, rid, new_len: int) -> List[int]:
         """Per group, how many pages a step that extends `rid` to `new_len` tokens must take."""
@@ -243,7 +244,7 @@ class CacheManager:
         req = self._requests[rid]
         req.length = new_len
         for gi, (g, held) in enumerate(zip(self.groups, req.blocks)):
-            if g.spec.window is None:
+            if g.spec.window is None and not g.spec.chunk:
                 continue
             first = min(self._first_needed_block(g, new_len), req.hi[gi])
             if req.lo[gi] < first:

@@ -15,6 +15,12 @@
 // otherwise all tokens 0 .. num_tokens - 1 are done.
 //
 // Head sizes: multiples of 8 up to 256.
+//
+// The extended entry point adds what other designs need, each a parameter:
+//   d_v, d_row   values of another size than the keys; both lie in cache rows of d_row elements
+//                (a multiple of 8 that holds either; what lies behind a row's d or d_v elements is zero)
+//   chunk        > 0: a query at position p sees the keys from (p / chunk) * chunk on, not from 0
+//   sink         1: the softmax's denominator holds one more unit, a key of score 0 without a value
 #include "common.cuh"
 
 namespace ifx {
@@ -60,8 +66,9 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ block_table, const int* __restrict__ positions,
                                          const int* __restrict__ token_req, const int* __restrict__ req_slot,
                                          const int* __restrict__ rows, T* __restrict__ out, int num_tokens, int nq,
-                                         int nkv, int d,
-                                         int page_size, int max_blocks, int num_pages, int window, float scale) {
+                                         int nkv, int d, int d_v, int d_row,
+                                         int page_size, int max_blocks, int num_pages, int window, int chunk,
+                                         int sink, float scale) {
   __shared__ __align__(16) float q_s[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * kWarpsPerBlock + warp;
@@ -71,17 +78,19 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
   const int pos = positions[t];
   const int slot = req_slot[token_req[t]];
   const int* table = block_table + (size_t)slot * max_blocks;
-  const size_t page_stride = (size_t)2 * nkv * page_size * d;       // elements per page (K and V)
-  const size_t head_off_k = (size_t)g * page_size * d;
-  const size_t head_off_v = ((size_t)nkv + g) * page_size * d;
+  const size_t page_stride = (size_t)2 * nkv * page_size * d_row;   // elements per page (K and V)
+  const size_t head_off_k = (size_t)g * page_size * d_row;
+  const size_t head_off_v = ((size_t)nkv + g) * page_size * d_row;
 
   const T* qrow = q + ((size_t)t * nq + h) * d;
-  for (int e = lane; e < d; e += 32) q_s[warp][e] = to_f32(qrow[e]);
+  for (int e = lane; e < d_row; e += 32) q_s[warp][e] = e < d ? to_f32(qrow[e]) : 0.0f;
   __syncwarp();
 
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  int first = window > 0 ? max(0, pos - window + 1) : 0;
+  if (chunk > 0) first = max(first, (pos / chunk) * chunk);
   const int end = pos + 1;
-  float m = -INFINITY, l = 0.0f;
+  // the sink is a key of score 0 that comes first and brings no value: maximum 0, sum 1
+  float m = sink ? 0.0f : -INFINITY, l = sink ? 1.0f : 0.0f;
   float acc[kMaxHeadDim / 32];
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
@@ -95,8 +104,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     if (valid) {
       page = table[j / page_size];
       if (page < 0 || page >= num_pages) page = 0;       // a broken table must not read outside the pool
-      row_off = (size_t)(j % page_size) * d;
-      s = dot_row<T>(q_s[warp], kv_pool + (size_t)page * page_stride + head_off_k + row_off, d) * scale;
+      row_off = (size_t)(j % page_size) * d_row;
+      s = dot_row<T>(q_s[warp], kv_pool + (size_t)page * page_stride + head_off_k + row_off, d_row) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = valid ? expf(s - m_new) : 0.0f;
@@ -114,16 +123,16 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 #pragma unroll
       for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int e = lane + 32 * i;
-        if (e < d) acc[i] = fmaf(pj, to_f32(vrow[e]), acc[i]);
+        if (e < d_v) acc[i] = fmaf(pj, to_f32(vrow[e]), acc[i]);
       }
     }
   }
   const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-  T* orow = out + ((size_t)t * nq + h) * d;
+  T* orow = out + ((size_t)t * nq + h) * d_v;
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int e = lane + 32 * i;
-    if (e < d) orow[e] = from_f32<T>(acc[i] * inv);
+    if (e < d_v) orow[e] = from_f32<T>(acc[i] * inv);
   }
 }
 
@@ -131,26 +140,38 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 
 using namespace ifx;
 
-extern "C" int ifx_attention_generic(const void* q, const void* kv_pool, const int* block_table,
-                                     const int* positions, const int* token_req, const int* req_slot,
-                                     const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int page_size,
-                                     int max_blocks, int num_pages, int window, float scale, int dtype,
-                                     cudaStream_t stream) {
+extern "C" int ifx_attention_generic_ex(const void* q, const void* kv_pool, const int* block_table,
+                                        const int* positions, const int* token_req, const int* req_slot,
+                                        const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int d_v,
+                                        int d_row, int page_size, int max_blocks, int num_pages, int window, int chunk,
+                                        int sink, float scale, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || d % 8 || d > kMaxHeadDim || page_size <= 0 || max_blocks <= 0)
+  if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || d_v <= 0 || d_row % 8 || d_row > kMaxHeadDim || d > d_row ||
+      d_v > d_row || page_size <= 0 || max_blocks <= 0 || chunk < 0)
     return IFX_E_BADARG;
   const long long items = (long long)num_tokens * nq;
   const unsigned blocks = (unsigned)((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
   if (dtype == IFX_DT_F32)
     attention_generic_kernel<float><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
         (const float*)q, (const float*)kv_pool, block_table, positions, token_req, req_slot, rows, (float*)out,
-        num_tokens, nq, nkv, d, page_size, max_blocks, num_pages, window, scale);
+        num_tokens, nq, nkv, d, d_v, d_row, page_size, max_blocks, num_pages, window, chunk, sink, scale);
   else if (dtype == IFX_DT_BF16)
     attention_generic_kernel<__nv_bfloat16><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, block_table, positions, token_req, req_slot,
-        rows, (__nv_bfloat16*)out, num_tokens, nq, nkv, d, page_size, max_blocks, num_pages, window, scale);
+        rows, (__nv_bfloat16*)out, num_tokens, nq, nkv, d, d_v, d_row, page_size, max_blocks, num_pages, window,
+        chunk, sink, scale);
   else
     return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();
   return 0;
+}
+
+extern "C" int ifx_attention_generic(const void* q, const void* kv_pool, const int* block_table,
+                                     const int* positions, const int* token_req, const int* req_slot,
+                                     const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int page_size,
+                                     int max_blocks, int num_pages, int window, float scale, int dtype,
+                                     cudaStream_t stream) {
+  if (d <= 0 || d % 8) return IFX_E_BADARG;
+  return ifx_attention_generic_ex(q, kv_pool, block_table, positions, token_req, req_slot, rows, out, num_tokens, nq,
+                                  nkv, d, d, d, page_size, max_blocks, num_pages, window, 0, 0, scale, dtype, stream);
 }

@@ -1,0 +1,190 @@
+// A mixture of small feed-forward experts: the router's choice and the experts' work for every token.
+//
+//   moe_route     scores = softmax(z) over all router outputs (float32); the `top` largest of score + correction
+//                 are chosen (the earlier index wins a tie); their weights are the scores themselves
+//   moe_up        act[p] = relu(W_up[e] h[t])^2 for every (token, choice) pair p = t * top + c whose expert e
+//                 has weights (experts numbered from `experts` on hand their input on unchanged)
+//   moe_down      out[t] = sum over the token's choices, in their order, of weight * (W_down[e] act[p]), or
+//                 weight * h[t] for an expert without weights
+//
+// These are the kernels of the float32 run and of steps with few tokens: a warp makes one output number as a dot
+// product (lanes stride the inner size, then a shuffle tree), so every sum has an order that depends on the sizes
+// alone.  Expert weights are stacked: up [experts, ff, width], down [experts, width, ff].
+#include "common.cuh"
+
+namespace ifx {
+
+constexpr int kMaxRouterOutputs = 1024;
+
+__global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction,
+                                 int* __restrict__ ids, float* __restrict__ weights, int T, int n, int top) {
+  __shared__ float score_s[4][kMaxRouterOutputs];
+  __shared__ float choice_s[4][kMaxRouterOutputs];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  const float* zr = z + (size_t)t * n;
+  float m = -INFINITY;
+  for (int i = lane; i < n; i += 32) m = fmaxf(m, zr[i]);
+  m = warp_max(m);
+  float sum = 0.0f;
+  for (int i = lane; i < n; i += 32) {
+    const float e = expf(zr[i] - m);
+    score_s[warp][i] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  for (int i = lane; i < n; i += 32) {
+    const float sc = score_s[warp][i] / sum;
+    score_s[warp][i] = sc;
+    choice_s[warp][i] = sc + (correction ? correction[i] : 0.0f);
+  }
+  __syncwarp();
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = lane; i < n; i += 32) {
+      const float v = choice_s[warp][i];
+      if (v > best) { best = v; at = i; }              // i ascends: the earlier index stays on a tie
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= n) at = 0;                               // only if every score is NaN
+    if (lane == 0) {
+      ids[(size_t)t * top + c] = at;
+      weights[(size_t)t * top + c] = score_s[warp][at];
+      choice_s[warp][at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float dot_lanes(const T* __restrict__ w, const float* __restrict__ a, int n, int lane) {
+  float s = 0.0f;
+  for (int i = lane; i < n; i += 32) s = fmaf(to_f32(w[i]), a[i], s);
+  return warp_sum(s);
+}
+
+constexpr int kMoeWarps = 8;
+
+template <typename T>
+__global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
+                              T* __restrict__ act, int top, int experts, int width, int ff, int rows_per_block) {
+  extern __shared__ float h_s[];
+  const int p = blockIdx.x;
+  const int e = ids[p];
+  if (e >= experts || e < 0) return;
+  const int t = p / top;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) h_s[i] = to_f32(h[(size_t)t * width + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.y * rows_per_block;
+  const T* w = w_up + (size_t)e * ff * width;
+  for (int f = f0 + warp; f < min(ff, f0 + rows_per_block); f += kMoeWarps) {
+    const float zf = fmaxf(dot_lanes<T>(w + (size_t)f * width, h_s, width, lane), 0.0f);
+    if (lane == 0) act[(size_t)p * ff + f] = from_f32<T>(zf * zf);
+  }
+}
+
+template <typename T, typename TO>
+__global__ void moe_down_kernel(const T* __restrict__ h, const T* __restrict__ act, const T* __restrict__ w_down,
+                                const int* __restrict__ ids, const float* __restrict__ weights, TO* __restrict__ out,
+                                int top, int experts, int width, int ff, int rows_per_block) {
+  extern __shared__ float a_s[];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = blockIdx.y * rows_per_block, c1 = min(width, c0 + rows_per_block);
+  float acc[8];                                         // rows c0 + warp + 8 r of this warp
+#pragma unroll
+  for (int r = 0; r < 8; ++r) acc[r] = 0.0f;
+  for (int c = 0; c < top; ++c) {
+    const int p = t * top + c;
+    const int e = ids[p];
+    const float g = weights[p];
+    if (e >= experts || e < 0) {                        // the input itself
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int row = c0 + warp + kMoeWarps * r;
+          if (row < c1) acc[r] = fmaf(g, to_f32(h[(size_t)t * width + row]), acc[r]);
+        }
+      }
+      continue;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < ff; i += blockDim.x) a_s[i] = to_f32(act[(size_t)p * ff + i]);
+    __syncthreads();
+    const T* w = w_down + (size_t)e * width * ff;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int row = c0 + warp + kMoeWarps * r;
+      if (row < c1) {
+        const float d = dot_lanes<T>(w + (size_t)row * ff, a_s, ff, lane);
+        acc[r] = fmaf(g, d, acc[r]);
+      }
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int row = c0 + warp + kMoeWarps * r;
+      if (row < c1) out[(size_t)t * width + row] = from_f32<TO>(acc[r]);
+    }
+  }
+}
+
+}  // namespace ifx
+
+using namespace ifx;
+
+extern "C" {
+
+int ifx_moe_route(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
+                  cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n <= 0 || top <= 0 || top > n) return IFX_E_BADARG;
+  if (n > kMaxRouterOutputs) return IFX_E_TOOBIG;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, correction, ids, weights, T, n, top);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+// h [T, width], act [T * top, ff] in `dtype`; out [T, width] in out_dtype.
+int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
+                    void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
+                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top <= 0 || experts < 0 || width <= 0 || ff <= 0) return IFX_E_BADARG;
+  if ((size_t)width * 4 > 160 * 1024 || (size_t)ff * 4 > 160 * 1024) return IFX_E_TOOBIG;
+  const int up_rows = 32, down_rows = 64;               // 64 = 8 warps x 8 rows
+  dim3 grid_up(T * top, (ff + up_rows - 1) / up_rows), grid_down(T, (width + down_rows - 1) / down_rows);
+  const size_t smem_up = (size_t)width * 4, smem_down = (size_t)ff * 4;
+#define IFX_MOE(TT, TO)                                                                                           \
+  do {                                                                                                            \
+    if (experts > 0) {                                                                                            \
+      auto up = moe_up_kernel<TT>;                                                                                \
+      if (smem_up > 48 * 1024) cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up); \
+      up<<<grid_up, kMoeWarps * 32, smem_up, stream>>>((const TT*)h, (const TT*)w_up, ids, (TT*)act, top, experts, \
+                                                       width, ff, up_rows);                                       \
+    }                                                                                                             \
+    auto down = moe_down_kernel<TT, TO>;                                                                          \
+    if (smem_down > 48 * 1024)                                                                                    \
+      cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);                    \
+    down<<<grid_down, kMoeWarps * 32, smem_down, stream>>>((const TT*)h, (const TT*)act, (const TT*)w_down, ids,  \
+                                                           weights, (TO*)out, top, experts, width, ff, down_rows); \
+  } while (0)
+  if (dtype == IFX_DT_F32 && out_dtype == IFX_DT_F32) IFX_MOE(float, float);
+  else if (dtype == IFX_DT_BF16 && out_dtype == IFX_DT_BF16) IFX_MOE(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == IFX_DT_BF16 && out_dtype == IFX_DT_F32) IFX_MOE(__nv_bfloat16, float);
+  else return IFX_E_DTYPE;
+#undef IFX_MOE
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

@@ -143,7 +143,9 @@ class CudaKernels:
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows",
                    "ifx_gemm_tcgen05", "ifx_postnorm_add_rmsnorm", "ifx_concat_cast", "ifx_xielu", "ifx_softcap",
                    "ifx_short_conv", "ifx_latent_norm_append", "ifx_latent_attention_generic", "ifx_latent_attention_mma",
-                   "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched", "ifx_gemm_skinny_act"):
+                   "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched", "ifx_gemm_skinny_act",
+                   "ifx_attention_generic_ex", "ifx_norm_rope_append", "ifx_token_shift_mix", "ifx_cast_rows",
+                   "ifx_wkv_scan", "ifx_moe_route", "ifx_moe_experts", "ifx_tanh_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
@@ -462,7 +464,7 @@ class CudaKernels:
         parts = None
         if type(block) is PreNormBlock:
             m, f, n1, n2 = block.mixer, block.ffn, block.norm_mixer, block.norm_ffn
-            if (type(m) is Attention and type(f) is SwiGLU and type(n1) is RMSNorm and type(n2) is RMSNorm
+            if (type(m) is Attention and not m.general and type(f) is SwiGLU and type(n1) is RMSNorm and type(n2) is RMSNorm
                     and m.hidden == f.hidden == n1.size == n2.size):
                 parts = (m, f, n1, n2)
         block._native_parts = parts
@@ -618,8 +620,15 @@ class CudaKernels:
             return 0
         return int(extra_len.get("attn.prefill_tiles", 0) == 0 and extra_len["attn.decode_rows"] * nkv * 8 <= 148)
 
-    def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
-        """`qkv`: the stacked projections [T, (nq + 2 nkv) d] as a tensor or a PartialSum."""
+    def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm=None, k_norm=None, norm_eps=0.0, dv=None,
+                    own_kv=True):
+        """`qkv`: the stacked projections [T, (nq + 2 nkv) d] as a tensor or a PartialSum.
+        With `q_norm` / `k_norm` (float32 [d]) every query / key head is RMS-normed with that weight before the
+        rotation; `dv`: the values' head size if it is not `d` (cache rows hold the larger of the two);
+        `own_kv` False: the rows hold queries only and nothing is stored."""
+        if q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv:
+            return self._norm_rope_append(qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm, k_norm, norm_eps,
+                                          d if dv is None else dv, own_kv)
         partial, splits = None, 0
         if isinstance(qkv, PartialSum):
             partial, splits, dtype, device = qkv.parts, qkv.splits, qkv.dtype, qkv.parts.device
@@ -646,11 +655,49 @@ class CudaKernels:
         self.launches += 1
         return q_out
 
-    def attention(self, q, nq, nkv, d, window, scale, ctx, cache):
+    def _norm_rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm, k_norm, norm_eps, dv, own_kv):
+        _need(bias is None, "rope_append: biases and head norms together are not built")
+        partial, splits = None, 0
+        if isinstance(qkv, PartialSum):
+            partial, splits, dtype, device = qkv.parts, qkv.splits, qkv.dtype, qkv.parts.device
+            T, width = qkv.shape
+            qkv = None
+        else:
+            dtype, device = qkv.dtype, qkv.device
+            T, width = qkv.shape
+        src_kv = nkv if own_kv else 0
+        _need(width == (nq + src_kv) * d + src_kv * dv, "rope_append: the rows' width does not fit the head counts")
+        for w in (q_norm, k_norm):
+            _need(w is None or (w.dtype == torch.float32 and w.numel() == d), "rope_append: a head norm weight is float32 [d]")
+        q_out = torch.empty((T, nq * d), dtype=dtype, device=device)
+        kv, table = cache.kv, cache.block_table
+        write = bool(own_kv and cache.writes and kv is not None)
+        d_row = d
+        if write:
+            _need(kv.dtype == dtype, f"rope_append: cache is {kv.dtype}, activations {dtype}")
+            d_row = kv.shape[-1]
+            _need(kv.shape[1] == 2 and kv.shape[2] == nkv and d_row >= max(d, dv), "rope_append: the cache does not fit the heads")
+        rot = 0 if rotary is None else int(rotary.rotary_dim)
+        _need(rot <= d, "rope_append: rotary_dim exceeds the head size")
+        _check(self.lib.ifx_norm_rope_append(
+            _ptr(qkv), _ptr(partial), splits, _ptr(q_norm), _ptr(k_norm), ctypes.c_float(norm_eps),
+            _ptr(None if rotary is None else rotary.inv_freq), rot,
+            int(bool(rotary.interleaved)) if rotary is not None else 0, _ptr(ctx.positions), _ptr(ctx.token_req),
+            _ptr(ctx.req_slot), _ptr(table), 0 if table is None else table.shape[1], cache.page_size,
+            0 if kv is None else kv.shape[0], _ptr(kv if write else None), _ptr(q_out), T, nq, src_kv, nkv, d, dv, d_row,
+            int(write), _DT[dtype], _stream()), "rope_append (normed heads)")
+        self.launches += 1
+        return q_out
+
+    def attention(self, q, nq, nkv, d, window, scale, ctx, cache, chunk=None, sink=False, dv=None):
         """Every token attends its request's keys up to its own position (or the last
         `window` of them) through the block table.  float32: the per-token kernel
         whose additions depend on the position only.  bfloat16: the tiled kernels,
-        one launch for the prompt portions and one for the single decoded tokens."""
+        one launch for the prompt portions and one for the single decoded tokens.
+        `chunk`: a query at position p sees keys from (p // chunk) * chunk on; `sink`: one more unit in the
+        softmax's denominator; `dv`: the values' head size if it is not `d`."""
+        if chunk or sink or (dv is not None and dv != d):
+            return self._attention_masked(q, nq, nkv, d, d if dv is None else dv, window, chunk, sink, scale, ctx, cache)
         T = q.shape[0]
         kv, table = cache.kv, cache.block_table
         _need(kv is not None and table is not None, "attention: the mixer has no key/value cache")
@@ -711,6 +758,25 @@ class CudaKernels:
             splits = 8
         return splits
 
+    def _attention_masked(self, q, nq, nkv, d, dv, window, chunk, sink, scale, ctx, cache):
+        """Attention with a chunk mask, a sink or values of their own size: the per-token kernel."""
+        T = q.shape[0]
+        kv, table = cache.kv, cache.block_table
+        _need(kv is not None and table is not None, "attention: the mixer has no key/value cache")
+        _need(kv.dtype == q.dtype, f"attention: cache is {kv.dtype}, queries {q.dtype}")
+        _need(q.is_contiguous() and q.shape[1] == nq * d, "attention: queries must be one [tokens, heads * size] block")
+        d_row = kv.shape[-1]
+        _need(kv.shape[1] == 2 and kv.shape[2] == nkv and d_row >= max(d, dv) and d_row % 8 == 0 and d_row <= 256,
+              "attention: the cache does not fit the heads")
+        out = torch.empty((T, nq * dv), dtype=q.dtype, device=q.device)
+        _check(self.lib.ifx_attention_generic_ex(
+            _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(None),
+            _ptr(out), T, nq, nkv, d, dv, d_row, cache.page_size, table.shape[1], kv.shape[0],
+            0 if window is None else int(window), int(chunk or 0), int(bool(sink)), ctypes.c_float(scale), _DT[q.dtype],
+            _stream()), "attention (masked)")
+        self.launches += 1
+        return out
+
     def _attention_generic(self, q, kv, table, ctx, rows, count, out, nq, nkv, d, common):
         _check(self.lib.ifx_attention_generic(
             _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot),
@@ -718,9 +784,11 @@ class CudaKernels:
         self.launches += 1
 
     # ------------------------------------------- layers that norm a sublayer's output
-    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, conv=None):
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, conv=None, cast_out=False):
         """x += y / rms(y) * w_post (x float32, in place).  With `w_next`, also returns the next norm of the
-        updated rows, x / rms(x) * w_next in `out_dtype`: sum and both norms in one kernel.  `conv` =
+        updated rows, x / rms(x) * w_next in `out_dtype`: sum and both norms in one kernel.  With `cast_out`
+        (and no `w_next`) it returns the updated rows themselves in `out_dtype`, for a sublayer that reads
+        x without a norm.  `conv` =
         (weight [hidden, taps], taps, state, index, ctx), allowed when every request of the step brings one token
         (`ctx.max_span == 1`): the rows come back as h + conv(h) over time, and the state has moved on."""
         splits = 1
@@ -733,7 +801,7 @@ class CudaKernels:
         _need(w_post.dtype == torch.float32 and (w_next is None or w_next.dtype == torch.float32),
               "postnorm_add: norm weights must be float32")
         T, H = x.shape
-        out = None if w_next is None else torch.empty((T, H), dtype=out_dtype or y.dtype, device=x.device)
+        out = None if (w_next is None and not cast_out) else torch.empty((T, H), dtype=out_dtype or y.dtype, device=x.device)
         cw, taps, st_ptr, stride, treq, rslot = None, 0, ctypes.c_void_p(0), 0, None, None
         if conv is not None:
             cw, taps, state, index, ctx = conv
@@ -901,6 +969,94 @@ class CudaKernels:
             splits, _stream()), "latent_attention (tiles)")
         self.launches += 1 + int(splits > 1)
         return self.linear_heads(olat, w_uv, heads, rank, vdim, w_is_nk=True)               # [T, heads * vdim]
+
+    # ------------------------------------------------- recurrence with matrix state
+    def cast_rows(self, x, dtype):
+        """float32 rows in the run's dtype (the rows themselves when that is float32)."""
+        if dtype == torch.float32:
+            return x
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "cast_rows: contiguous float32 rows")
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        _check(self.lib.ifx_cast_rows(_ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _DT[dtype], _stream()), "cast_rows")
+        self.launches += 1
+        return out
+
+    def tanh(self, z):
+        """tanh of every element, in place."""
+        _need(z.is_contiguous(), "tanh: contiguous input")
+        _check(self.lib.ifx_tanh_rows(_ptr(z), ctypes.c_longlong(z.numel()), _DT[z.dtype], _stream()), "tanh")
+        self.launches += 1
+        return z
+
+    def token_shift_mix(self, x, mu, state, prev_offset, ctx, out_dtype):
+        """mixes[m, t] = x[t] + (x[t - 1] - x[t]) * mu[m] for the float32 rows `x` [T, C] and `mu` [M, C]; the row
+        before a span's first one is `state[slot, prev_offset : prev_offset + C]` (float32; zeros at a sequence's
+        start).  The state is not changed here: `wkv_scan` leaves the step's last row there."""
+        T, C = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and mu.dtype == torch.float32 and mu.is_contiguous()
+              and mu.shape[1] == C, "token_shift_mix: float32 rows and weights of one width")
+        _need(state is not None and state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+              and prev_offset + C <= state.shape[1], "token_shift_mix: the state does not hold a row")
+        out = torch.empty((mu.shape[0], T, C), dtype=out_dtype, device=x.device)
+        _check(self.lib.ifx_token_shift_mix(
+            _ptr(x), _ptr(mu), ctypes.c_void_p(state.data_ptr() + 4 * prev_offset), ctypes.c_longlong(state.shape[1]),
+            _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out), T, C, mu.shape[0], _DT[out_dtype],
+            _stream()), "token_shift_mix")
+        self.launches += 1
+        return out
+
+    def wkv_scan(self, r, k, v, w_raw, g, w0, u, norm_w, eps, heads, dim, state, prev_offset, x, ctx, out_dtype):
+        """The recurrence of csrc/wkv.cu over every request's tokens.  r, k, v, w_raw, g: float32 [T, heads * dim];
+        `state`: float32 [slots, heads * dim * dim + C], the matrices first, then the last input row, both moved on.
+        Returns out / rms(out) per head * norm_w * silu(g) in `out_dtype`."""
+        T, HD = r.shape
+        C = x.shape[1]
+        for t in (r, k, v, w_raw, g):
+            _need(t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (T, HD), "wkv_scan: float32 [T, heads * dim] inputs")
+        for t in (w0, u, norm_w):
+            _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == HD, "wkv_scan: float32 constants of heads * dim")
+        _need(HD == heads * dim and prev_offset == heads * dim * dim and state.dtype == torch.float32 and state.is_contiguous()
+              and state.dim() == 2 and state.shape[1] == prev_offset + C and x.dtype == torch.float32 and x.is_contiguous(),
+              "wkv_scan: the state does not fit the sizes")
+        scratch = torch.empty((T, HD), dtype=torch.float32, device=r.device)
+        y = torch.empty((T, HD), dtype=out_dtype, device=r.device)
+        _check(self.lib.ifx_wkv_scan(
+            _ptr(r), _ptr(k), _ptr(v), _ptr(w_raw), _ptr(g), _ptr(w0), _ptr(u), _ptr(norm_w), ctypes.c_float(eps),
+            _ptr(state), ctypes.c_void_p(state.data_ptr() + 4 * prev_offset), ctypes.c_longlong(state.shape[1]), _ptr(x), C,
+            _ptr(ctx.cu_seqlens), _ptr(ctx.req_slot), _ptr(scratch), _ptr(y), ctx.num_requests, heads, dim, _DT[out_dtype],
+            _stream()), "wkv_scan")
+        self.launches += 1
+        return y
+
+    # ------------------------------------------------------- mixture of experts
+    def moe_route(self, z, correction, top):
+        """(ids int32 [T, top], weights float32 [T, top]) from router logits z float32 [T, n]: softmax scores; the
+        `top` largest of score + correction are chosen, their weights are the scores."""
+        T, n = z.shape
+        _need(z.dtype == torch.float32 and z.is_contiguous() and (correction is None or (correction.dtype == torch.float32
+              and correction.numel() == n)), "moe_route: float32 logits and corrections")
+        ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=z.device)
+        _check(self.lib.ifx_moe_route(_ptr(z), _ptr(correction), _ptr(ids), _ptr(weights), T, n, int(top), _stream()), "moe_route")
+        self.launches += 1
+        return ids, weights
+
+    def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype):
+        """sum over a token's choices of weight * W_down[e] relu(W_up[e] h)^2, or weight * h for e >= experts.
+        w_up [experts, ff, width], w_down [experts, width, ff] in h's dtype."""
+        T, width = h.shape
+        top = ids.shape[1]
+        ff = w_up.shape[1] if experts else 1
+        _need(h.is_contiguous() and (not experts or (w_up.dtype == h.dtype and w_down.dtype == h.dtype and w_up.is_contiguous()
+              and w_down.is_contiguous() and tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff))),
+              "moe_experts: stacked expert weights in the activations' dtype")
+        act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+        out = torch.empty((T, width), dtype=out_dtype, device=h.device)
+        _check(self.lib.ifx_moe_experts(_ptr(h), _ptr(w_up if experts else None), _ptr(w_down if experts else None), _ptr(ids),
+                                        _ptr(weights), _ptr(act), _ptr(out), T, top, int(experts), width, ff, _DT[h.dtype],
+                                        _DT[out_dtype], _stream()), "moe_experts")
+        self.launches += 2 if experts else 1
+        return out
 
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):

@@ -3,6 +3,7 @@
 //
 //   postnorm_add_rmsnorm   x += y / rms(y) * w_post           (x float32, in place)
 //                          h  = x / rms(x) * w_next           (optional second stage)
+//                          h  = x in the output's dtype       (out given, w_next null: the next sublayer reads x itself)
 //                          y may arrive as the float32 partial sums [splits, rows, hidden] of a K-split product
 //   concat_cast            out[t] = [a[t]; b[t]] in the run's dtype, a and b float32
 //   xielu                  z -> a_pos z^2 + z/2 (z > 0), a_neg (e^z - 1 - z) + z/2 (z <= 0)
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(1024) postnorm_add_rmsnorm_kernel(
     const int i = threadIdx.x + j * blockDim.x;
     x_pre[j] = i < hidden ? xr[i] : 0.0f;
     wp_pre[j] = i < hidden ? w_post[i] : 0.0f;
-    wn_pre[j] = (i < hidden && out != nullptr) ? w_next[i] : 0.0f;
+    wn_pre[j] = (i < hidden && out != nullptr && w_next != nullptr) ? w_next[i] : 0.0f;
   }
   // the convolution's taps and the request's state do not depend on a reduction either (up to 4 taps: 3 cells)
   const bool conv_pre = conv.w != nullptr && conv.taps <= 4;
@@ -94,9 +95,13 @@ __global__ void __launch_bounds__(1024) postnorm_add_rmsnorm_kernel(
   }
   for (int i = threadIdx.x + PRE * blockDim.x; i < hidden; i += blockDim.x) add_row(i, xr[i], w_post[i]);
   if (out == nullptr) return;
+  TO* o = out + row * hidden;
+  if (w_next == nullptr) {                               // no second norm: the updated row in the output's dtype
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<TO>(row_s[i]);
+    return;
+  }
   ss2 = block_sum(ss2, scratch);
   const float r2 = rsqrtf(ss2 / (float)hidden + eps_next);
-  TO* o = out + row * hidden;
   if (conv.w == nullptr) {
 #pragma unroll
     for (int j = 0; j < PRE; ++j) {
@@ -200,9 +205,13 @@ __global__ void __launch_bounds__(256) postnorm_add_rmsnorm_rows_kernel(
     ss2 = fmaf(v.x, v.x, ss2); ss2 = fmaf(v.y, v.y, ss2); ss2 = fmaf(v.z, v.z, ss2); ss2 = fmaf(v.w, v.w, ss2);
   }
   if (out == nullptr) return;
+  TO* o = out + row * hidden;
+  if (w_next == nullptr) {
+    for (int i = threadIdx.x * 4; i < hidden; i += step) st4(o + i, ld4(row_s + i));
+    return;
+  }
   ss2 = block_sum(ss2, scratch);
   const float r2 = rsqrtf(ss2 / (float)hidden + eps_next);
-  TO* o = out + row * hidden;
   for (int i = threadIdx.x * 4; i < hidden; i += step) {
     const float4 v = ld4(row_s + i), wv = ld4(w_next + i);
     st4(o + i, make_float4(v.x * r2 * wv.x, v.y * r2 * wv.y, v.z * r2 * wv.z, v.w * r2 * wv.w));
@@ -296,7 +305,7 @@ int ifx_postnorm_add_rmsnorm(float* x, const void* y, const float* w_post, float
   const bool rows_path = !exact && T > 512 && conv_w == nullptr && hidden % 4 == 0 && (uintptr_t)x % 16 == 0 &&
                          (uintptr_t)y % 16 == 0 && (out == nullptr || (uintptr_t)out % 16 == 0) &&
                          (uintptr_t)w_post % 16 == 0 && (w_next == nullptr || (uintptr_t)w_next % 16 == 0);
-  if (out != nullptr && w_next == nullptr) return IFX_E_BADARG;
+  if (conv_w != nullptr && w_next == nullptr) return IFX_E_BADARG;
 #define IFX_LAUNCH(TY, TO)                                                                                         \
   do {                                                                                                             \
     if (rows_path) {                                                                                               \

@@ -221,6 +221,93 @@ rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __re
   }
 }
 
+
+// The general form for designs whose heads are normed before they are turned, whose values have a size of
+// their own, or whose layer stores nothing: one block per (token, head).
+//
+//   qkv row = [nq heads of d | nkv_src key heads of d | nkv_src value heads of d_v]     (nkv_src may be 0)
+//   query and key heads: x / sqrt(mean(x^2) + eps) * w over the head's d elements (w shared by all heads;
+//   null: no norm), in float32, before the rotation; then the rotation of the first `rot` elements
+//   cache rows have d_row elements (>= d, >= d_v); a key fills the first d, a value the first d_v
+template <typename T>
+__global__ void norm_rope_append_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_partial, int num_splits,
+                                        size_t split_stride, const float* __restrict__ q_norm_w,
+                                        const float* __restrict__ k_norm_w, float norm_eps,
+                                        const float* __restrict__ inv_freq, int rot, int interleaved,
+                                        const int* __restrict__ positions, const int* __restrict__ token_req,
+                                        const int* __restrict__ req_slot, const int* __restrict__ block_table,
+                                        int max_blocks, int page_size, int num_pages, T* __restrict__ kv_pool,
+                                        T* __restrict__ q_out, int nq, int nkv_src, int nkv_cache, int d, int d_v,
+                                        int d_row, int write_cache) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;                      // [0, nq) q, [nq, nq + nkv_src) k, then v
+  const bool is_q = head < nq, is_v = head >= nq + nkv_src;
+  const int width = (nq + nkv_src) * d + nkv_src * d_v;
+  const int size = is_v ? d_v : d;
+  const size_t src_off = (size_t)t * width + (is_v ? (size_t)(nq + nkv_src) * d + (size_t)(head - nq - nkv_src) * d_v
+                                                   : (size_t)head * d);
+  const int pos = positions[t];
+  T* dst = nullptr;
+  if (is_q) {
+    dst = q_out + ((size_t)t * nq + head) * d;
+  } else if (write_cache) {
+    const int g = head - nq - (is_v ? nkv_src : 0);
+    const int slot = req_slot[token_req[t]];
+    const int page = block_table[(size_t)slot * max_blocks + pos / page_size];
+    if (page >= 0 && page < num_pages)              // never write outside the pool
+      dst = kv_pool + ((((size_t)page * 2 + (is_v ? 1 : 0)) * nkv_cache + g) * page_size + (pos % page_size)) * d_row;
+  }
+  auto load = [&](int e) -> float {                 // one element, the slices of a K-split product added in order
+    if (qkv_partial == nullptr) return to_f32(qkv[src_off + e]);
+    float a = 0.0f;
+    for (int s0 = 0; s0 < num_splits; ++s0) a += __ldcg(qkv_partial + (size_t)s0 * split_stride + src_off + e);
+    return a;
+  };
+  const float* nw = is_q ? q_norm_w : (is_v ? nullptr : k_norm_w);
+  float inv_rms = 1.0f;
+  if (nw != nullptr) {                              // every thread of the block takes part in the sum
+    float ss = 0.0f;
+    for (int e = threadIdx.x; e < size; e += blockDim.x) {
+      const float v = load(e);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    inv_rms = 1.0f / sqrtf(ss / (float)size + norm_eps);
+  }
+  if (dst == nullptr) return;
+  const int half_rot = is_v ? 0 : rot / 2;
+  for (int j = threadIdx.x; j < (size + 1) / 2; j += blockDim.x) {
+    int e0, e1;
+    if (j < half_rot) {
+      e0 = interleaved ? 2 * j : j;
+      e1 = interleaved ? 2 * j + 1 : j + half_rot;
+    } else {
+      e0 = 2 * half_rot + 2 * (j - half_rot);
+      e1 = e0 + 1;
+    }
+    float a = load(e0), c = e1 < size ? load(e1) : 0.0f;
+    if (nw != nullptr) {
+      a = a * inv_rms * nw[e0];
+      if (e1 < size) c = c * inv_rms * nw[e1];
+    }
+    if (j < half_rot) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
+      const float ra = a * cs - c * sn;
+      const float rc = c * cs + a * sn;
+      a = ra;
+      c = rc;
+    }
+    if (!is_q) {                      // the cache only ever holds finite values
+      a = isfinite(a) ? a : 0.0f;
+      c = isfinite(c) ? c : 0.0f;
+    }
+    dst[e0] = from_f32<T>(a);
+    if (e1 < size) dst[e1] = from_f32<T>(c);
+  }
+}
+
 }  // namespace ifx
 
 using namespace ifx;
@@ -263,4 +350,41 @@ extern "C" int ifx_rope_append(const void* qkv, const float* qkv_partial, int nu
                       interleaved, positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages,
                       (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv, d, write_cache, early_dependents);
   return IFX_E_DTYPE;
+}
+
+// See norm_rope_append_kernel.  nkv_src: key/value heads in the rows of qkv (0: the layer reads another layer's
+// cache and projects queries only); nkv_cache: key/value heads of the cache's pages.
+extern "C" int ifx_norm_rope_append(const void* qkv, const float* qkv_partial, int num_splits, const float* q_norm_w,
+                                    const float* k_norm_w, float norm_eps, const float* inv_freq, int rot,
+                                    int interleaved, const int* positions, const int* token_req, const int* req_slot,
+                                    const int* block_table, int max_blocks, int page_size, int num_pages, void* kv_pool,
+                                    void* q_out, int num_tokens, int nq, int nkv_src, int nkv_cache, int d, int d_v,
+                                    int d_row, int write_cache, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (nq <= 0 || nkv_src < 0 || d <= 0 || d_v <= 0 || rot < 0 || rot > d || rot % 2) return IFX_E_BADARG;
+  if (rot > 0 && inv_freq == nullptr) return IFX_E_BADARG;
+  if (write_cache && (nkv_src <= 0 || nkv_cache != nkv_src || page_size <= 0 || max_blocks <= 0 || kv_pool == nullptr ||
+                      d_row < d || d_row < d_v))
+    return IFX_E_BADARG;
+  if (nq + 2 * nkv_src > 65535) return IFX_E_TOOBIG;
+  if ((qkv == nullptr) == (qkv_partial == nullptr)) return IFX_E_BADARG;
+  if (qkv_partial != nullptr && num_splits <= 0) return IFX_E_BADARG;
+  const size_t split_stride = (size_t)num_tokens * ((size_t)(nq + nkv_src) * d + (size_t)nkv_src * d_v);
+  dim3 grid(num_tokens, nq + 2 * nkv_src);
+  const int longest = d > d_v ? d : d_v;
+  const int threads = longest / 2 > 64 ? 128 : (longest / 2 > 32 ? 64 : 32);
+  if (dtype == IFX_DT_F32)
+    norm_rope_append_kernel<float><<<grid, threads, 0, stream>>>(
+        (const float*)qkv, qkv_partial, num_splits, split_stride, q_norm_w, k_norm_w, norm_eps, inv_freq, rot,
+        interleaved, positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages, (float*)kv_pool,
+        (float*)q_out, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache);
+  else if (dtype == IFX_DT_BF16)
+    norm_rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, qkv_partial, num_splits, split_stride, q_norm_w, k_norm_w, norm_eps, inv_freq, rot,
+        interleaved, positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages,
+        (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache);
+  else
+    return IFX_E_DTYPE;
+  IFX_CHECK_LAUNCH();
+  return 0;
 }

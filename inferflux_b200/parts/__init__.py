@@ -2,7 +2,7 @@
 from .base import (Block, FeedForward, KVCacheSpec, Mixer, Norm, NormedDelta, Part, PositionEncoding, RotaryTable,
                    StateSpec, StreamMerge, TimeConv, WeightBuffers, build_part, register_part, registered_parts,
                    settle_pending)
-from . import attention, block, conv, embedding, latent_attention, mlp, norm, rope  # noqa: F401  (registration)
+from . import attention, block, conv, embedding, latent_attention, mlp, moe, norm, rope, wkv  # noqa: F401  (registration)
 
 __all__ = ["Block", "FeedForward", "KVCacheSpec", "Mixer", "Norm", "NormedDelta", "Part", "PositionEncoding",
            "RotaryTable", "StateSpec", "StreamMerge", "TimeConv", "WeightBuffers", "build_part", "register_part",

@@ -10,6 +10,12 @@ own position, or the last `window` of them (runtime/backends/cuda/kernels/
 flash_attention.cu:71-86, 152-172); then the output projection.
 
 The three projections are stacked at load so that one product makes q, k and v.
+
+Options that other designs use, all off by default: values of their own head size (`v_head_dim`), an RMS
+norm of every query and key head before the rotation with one weight per side (`qk_norm`), a mask in
+chunks (`chunk`: position p sees the keys from (p // chunk) * chunk on), one more unit in the softmax's
+denominator (`sink`), a layer that projects queries only and reads the keys and values another layer's
+cache holds (`own_kv` False), and other tensor names (`names`).
 """
 from __future__ import annotations
 
@@ -26,7 +32,13 @@ class Attention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (None or int),
     position (a PartSpec of role `position`, or None), qkv_bias (True, False or
     "if_present"), invent_bias (with "if_present": whether random-weights mode makes
-    the biases up; default True), scale (None for 1/sqrt(head_dim))."""
+    the biases up; default True), scale (None for 1/sqrt(head_dim)), v_head_dim (None: head_dim),
+    qk_norm (None, or {eps}), chunk (None or int), sink (bool), own_kv (default True),
+    names (tensor names of q, k, v, o, q_bias, k_bias, v_bias, q_norm, k_norm)."""
+
+    _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+              "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
 
     takes_scaled_rows = True          # h goes only into the stacked projection
 
@@ -44,7 +56,14 @@ class Attention(Mixer):
         self.nq = int(p["num_heads"])
         self.nkv = int(p["num_kv_heads"])
         self.d = int(p["head_dim"])
-        self.check_head_dim(self.d)
+        self.dv = int(p["v_head_dim"]) if p.get("v_head_dim") is not None else self.d
+        self.general = any(p.get(k) for k in ("qk_norm", "chunk", "sink")) or self.dv != self.d or not p.get("own_kv", True)
+        if self.general:                   # the general kernels take any even size up to 256
+            for size in (self.d, self.dv):
+                if size <= 0 or size % 2 or size > 256:
+                    raise ValueError(f"attention: head size {size} is not supported (even sizes up to 256)")
+        else:
+            self.check_head_dim(self.d)
         if self.nq % self.nkv:
             raise ValueError(f"attention: {self.nq} heads are not a multiple of {self.nkv} kv heads")
         self.window = None if p.get("window") is None else int(p["window"])
@@ -53,46 +72,86 @@ class Attention(Mixer):
         self.invent_bias = bool(p.get("invent_bias", True))
         pos = p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
-        self.w_qkv = self.b_qkv = self.w_o = None
+        self.qk_norm_eps = None if not p.get("qk_norm") else float(p["qk_norm"]["eps"])
+        self.chunk = None if not p.get("chunk") else int(p["chunk"])
+        if self.chunk is not None and self.chunk <= 0:
+            raise ValueError(f"attention: chunk must be positive, got {self.chunk}")
+        self.sink = bool(p.get("sink", False))
+        self.own_kv = bool(p.get("own_kv", True))
+        if self.general and self.qkv_bias == "if_present":
+            self.qkv_bias = False
+        if self.general and self.qkv_bias:
+            raise ValueError("attention: biases together with head norms, chunks, a sink or a shared cache are not built")
+        self.names = dict(self._NAMES)
+        self.names.update(p.get("names") or {})
+        self.w_qkv = self.b_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 
     # ---------------------------------------------------------------- declarations
     def cache_spec(self):
-        return KVCacheSpec(self.nkv, self.d, self.window)
+        """Rows that hold a key or a value, whichever is longer (a multiple of 8 elements); the cache of a layer
+        that stores nothing is never asked for (its schedule entry names the storing layer's)."""
+        row = self.d if not self.general else -(-max(self.d, self.dv) // 8) * 8
+        return KVCacheSpec(self.nkv, row, self.window, chunk=self.retain_chunk)
+
+    # The stretch of positions after which the cache may drop pages: the mask's own chunk, unless the
+    # configuration says that a reader of this cache looks further back (it then sets this to None).
+    @property
+    def retain_chunk(self):
+        return self.spec.params.get("retain_chunk", self.chunk)
+
+    def _sizes(self):
+        """Rows of the stacked projection: (query rows, key rows, value rows)."""
+        kv = self.nkv if self.own_kv else 0
+        return self.nq * self.d, kv * self.d, kv * self.dv
 
     def param_specs(self):
-        q, kv = self.nq * self.d, self.nkv * self.d
-        specs = {
-            "q_proj.weight": TensorSpec((q, self.hidden)),
-            "k_proj.weight": TensorSpec((kv, self.hidden)),
-            "v_proj.weight": TensorSpec((kv, self.hidden)),
-            "o_proj.weight": TensorSpec((self.hidden, q)),
-        }
+        n = self.names
+        q, k, v = self._sizes()
+        specs = {n["q"]: TensorSpec((q, self.hidden)), n["o"]: TensorSpec((self.hidden, self.nq * self.dv))}
+        if self.own_kv:
+            specs[n["k"]] = TensorSpec((k, self.hidden))
+            specs[n["v"]] = TensorSpec((v, self.hidden))
         if self.qkv_bias is not False:
             optional = self.qkv_bias == "if_present"
-            for n, size in (("q", q), ("k", kv), ("v", kv)):
-                specs[n + "_proj.bias"] = TensorSpec((size,), optional=optional, invent=self.invent_bias)
+            for side, size in (("q", q), ("k", k), ("v", v)):
+                specs[n[side + "_bias"]] = TensorSpec((size,), optional=optional, invent=self.invent_bias)
+        if self.qk_norm_eps is not None:
+            specs[n["q_norm"]] = TensorSpec((self.d,), init="ones")
+            if self.own_kv:
+                specs[n["k_norm"]] = TensorSpec((self.d,), init="ones")
         return specs
 
     def load(self, tensors, dtype, device):
-        q, kv = self.nq * self.d, self.nkv * self.d
-        has_bias = any((n + "_proj.bias") in tensors for n in ("q", "k", "v"))
-        layout = {"w_qkv": ((q + 2 * kv, self.hidden), dtype), "w_o": ((self.hidden, q), dtype)}
+        n = self.names
+        q, k, v = self._sizes()
+        sides = [("q", q)] + ([("k", k), ("v", v)] if self.own_kv else [])
+        has_bias = any(n[side + "_bias"] in tensors for side, _ in sides)
+        layout = {"w_qkv": ((q + k + v, self.hidden), dtype), "w_o": ((self.hidden, self.nq * self.dv), dtype)}
         if has_bias:
-            layout["b_qkv"] = ((q + 2 * kv,), torch.float32)              # added in float32
+            layout["b_qkv"] = ((q + k + v,), torch.float32)               # added in float32
+        if self.qk_norm_eps is not None:
+            layout["q_norm"] = ((self.d,), torch.float32)
+            layout["k_norm"] = ((self.d,), torch.float32)
         self.buffers = buf = WeightBuffers(device, layout)
         at = 0
-        for n, size in zip(("q", "k", "v"), (q, kv, kv)):                 # each projection into its rows of the stack
-            buf["w_qkv"][at:at + size].copy_(tensors[n + "_proj.weight"])
+        for side, size in sides:                                          # each projection into its rows of the stack
+            buf["w_qkv"][at:at + size].copy_(tensors[n[side]])
             if has_bias:
-                b = tensors.get(n + "_proj.bias")
+                b = tensors.get(n[side + "_bias"])
                 if b is None:
                     buf["b_qkv"][at:at + size].zero_()
                 else:
                     buf["b_qkv"][at:at + size].copy_(b)
             at += size
-        buf["w_o"].copy_(tensors["o_proj.weight"])
+        buf["w_o"].copy_(tensors[n["o"]])
         self.w_qkv, self.w_o = buf["w_qkv"], buf["w_o"]
         self.b_qkv = buf["b_qkv"] if has_bias else None
+        if self.qk_norm_eps is not None:
+            buf["q_norm"].copy_(tensors[n["q_norm"]])
+            self.q_norm_w = buf["q_norm"]
+            if self.own_kv:
+                buf["k_norm"].copy_(tensors[n["k_norm"]])
+                self.k_norm_w = buf["k_norm"]
 
     def step_sections(self, ctx):
         """The work lists of the kernel table's attention kernels, if it has any."""
@@ -104,6 +163,14 @@ class Attention(Mixer):
         k = ctx.kernels
         qkv = k.linear(h, self.w_qkv, allow_partial=True)                    # [T, (nq + 2 nkv) d], maybe in K slices
         rotary = self.position.rotary(ctx.device) if self.position is not None else None
-        q = k.rope_append(qkv, self.b_qkv, rotary, self.nq, self.nkv, self.d, ctx, cache)   # [T, nq d]
-        a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache)  # [T, nq d]
+        if not self.general:
+            q = k.rope_append(qkv, self.b_qkv, rotary, self.nq, self.nkv, self.d, ctx, cache)   # [T, nq d]
+            a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache)  # [T, nq d]
+            return k.linear(a, self.w_o, allow_partial=True)
+        if self.own_kv != bool(cache.writes):
+            raise ValueError("attention: a layer with keys and values of its own writes its cache, one without reads another's")
+        q = k.rope_append(qkv, None, rotary, self.nq, self.nkv, self.d, ctx, cache, q_norm=self.q_norm_w,
+                          k_norm=self.k_norm_w, norm_eps=self.qk_norm_eps or 0.0, dv=self.dv, own_kv=self.own_kv)
+        a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache, chunk=self.chunk,
+                        sink=self.sink, dv=self.dv)                                             # [T, nq dv]
         return k.linear(a, self.w_o, allow_partial=True)

@@ -38,11 +38,13 @@ class KVCacheSpec:
     """What a mixer stores per token: keys and values of `num_kv_heads` heads of
     `head_dim`; `window` None keeps every key, an integer only the last `window`.
     `planes` 2 stores keys and values; 1 stores one vector per head that serves as
-    both (a latent from which keys and values are made)."""
+    both (a latent from which keys and values are made).  `chunk`: positions are cut into stretches of that
+    many and no query ever reads a key of an earlier stretch than its own, so those pages can go."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -129,6 +131,9 @@ class Part:
     # `linear_swiglu`: the norm in front may then leave its row scale to that product
     # (`h` arrives as the kernels' pre-normed rows instead of a tensor).
     takes_scaled_rows = False
+    # True for a mixer or feed-forward that wants the float32 residual stream itself as its input (it reads it and
+    # leaves it alone) instead of its rounding to the run's dtype.
+    takes_stream = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

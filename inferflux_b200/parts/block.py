@@ -111,6 +111,52 @@ class SandwichBlock(Block):
         return x, NormedDelta(y, self.postnorm_ffn.weight, self.postnorm_ffn.eps)
 
 
+@register_part("block", "postnorm")
+class PostNormBlock(Block):
+    """A norm on each sublayer's output only; the sublayers read the residual stream itself:
+
+        x += norm_a(mixer(x));   x += norm_b(ffn(x))
+
+    params: ffn (False: the layer ends after the mixer).  Parts: mixer, postnorm_mixer and, with a feed-forward,
+    ffn, postnorm_ffn.  A sublayer's output travels unadded with its norm (`NormedDelta`); the sum, that norm
+    and the rounding of x to the run's dtype for the next sublayer are one kernel.  A sublayer that sets
+    `takes_stream` gets the float32 rows themselves."""
+
+    def __init__(self, spec, parts):
+        self.has_ffn = bool(spec.params.get("ffn", True))
+        names = {"mixer": "mixer", "postnorm_mixer": "norm"}
+        if self.has_ffn:
+            names.update({"ffn": "ffn", "postnorm_ffn": "norm"})
+        self.sub_parts = names
+        super().__init__(spec, parts)
+        for name, role in names.items():
+            if role == "norm" and not isinstance(parts[name], RMSNorm):
+                raise ValueError(f"postnorm block: {name} must be an RMS norm (its weight and eps go into a fused kernel)")
+
+    @staticmethod
+    def _sublayer_input(x, pending, reader, ctx):
+        """Settle what is pending and give the reader its rows."""
+        k = ctx.kernels
+        as_stream = reader.takes_stream or ctx.dtype == torch.float32
+        if isinstance(pending, NormedDelta):
+            if as_stream:
+                pending.add_to(x, ctx)
+                return x
+            return k.postnorm_add(x, pending.y, pending.weight, pending.eps, out_dtype=ctx.dtype, cast_out=True)
+        settle_pending(x, pending, ctx)
+        return x if as_stream else k.cast_rows(x, ctx.dtype)
+
+    def forward(self, x, pending, ctx, cache):
+        h = self._sublayer_input(x, pending, self.mixer, ctx)
+        y = self.mixer.forward(h, ctx, cache)
+        pending = NormedDelta(y, self.postnorm_mixer.weight, self.postnorm_mixer.eps)
+        if not self.has_ffn:
+            return x, pending
+        h = self._sublayer_input(x, pending, self.ffn, ctx)
+        y = self.ffn.forward(h, ctx)
+        return x, NormedDelta(y, self.postnorm_ffn.weight, self.postnorm_ffn.eps)
+
+
 @register_part("merge", "linear_reinject")
 class LinearReinject(StreamMerge):
     """x' = W [x; x0] + step[repeat]: the stream and the embedding output side by side through one matrix

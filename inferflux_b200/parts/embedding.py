@@ -17,28 +17,41 @@ from .base import Part, register_part
 
 @register_part("embedding", "embedding")
 class Embedding(Part):
-    """params: vocab_size, hidden_size, tensor_name (default `weight`)."""
+    """params: vocab_size, hidden_size, tensor_name (default `weight`), norm (None, or {tensor_name, eps}:
+    the gathered rows are RMS-normed with that weight, in float32, before they become the residual stream)."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.tensor_name = str(spec.params.get("tensor_name", "weight"))
-        self.table = None
+        norm = spec.params.get("norm")
+        self.norm_name = None if not norm else str(norm.get("tensor_name", "norm.weight"))
+        self.norm_eps = float(norm["eps"]) if norm else 0.0
+        self.table = self.norm_weight = None
 
     def param_specs(self):
-        return {self.tensor_name: TensorSpec((self.vocab, self.hidden))}
+        specs = {self.tensor_name: TensorSpec((self.vocab, self.hidden))}
+        if self.norm_name is not None:
+            specs[self.norm_name] = TensorSpec((self.hidden,), init="ones")
+        return specs
 
     def load(self, tensors, dtype, device):
         self.table = tensors[self.tensor_name].to(device=device, dtype=dtype).contiguous()
+        if self.norm_name is not None:
+            self.norm_weight = tensors[self.norm_name].to(device=device, dtype=torch.float32).contiguous()
 
     def forward(self, ctx):
-        return ctx.kernels.embed(self.table, ctx.token_ids, self.vocab)
+        x = ctx.kernels.embed(self.table, ctx.token_ids, self.vocab)
+        if self.norm_weight is not None:
+            x = ctx.kernels.rmsnorm(x, self.norm_weight, self.norm_eps, torch.float32)
+        return x
 
 
 @register_part("lm_head", "lm_head")
 class LMHead(Part):
-    """params: vocab_size, hidden_size, tied, softcap (None, or c: logits become c tanh(logits / c))."""
+    """params: vocab_size, hidden_size, tied, softcap (None, or c: logits become c tanh(logits / c)),
+    tensor_name (default `weight`)."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -49,10 +62,11 @@ class LMHead(Part):
         self.softcap = None if cap is None else float(cap)
         if self.softcap is not None and not self.softcap > 0:
             raise ValueError(f"lm_head: softcap must be positive, got {self.softcap}")
+        self.tensor_name = str(spec.params.get("tensor_name", "weight"))
         self.weight = None
 
     def param_specs(self):
-        return {"weight": TensorSpec((self.vocab, self.hidden), ignored=self.tied)}
+        return {self.tensor_name: TensorSpec((self.vocab, self.hidden), ignored=self.tied)}
 
     def load(self, tensors, dtype, device, tied_table=None):
         if self.tied:
@@ -60,7 +74,7 @@ class LMHead(Part):
                 raise ValueError("lm_head: tied head needs the embedding table")
             self.weight = tied_table
         else:
-            self.weight = tensors["weight"].to(device=device, dtype=dtype).contiguous()
+            self.weight = tensors[self.tensor_name].to(device=device, dtype=dtype).contiguous()
 
     def forward(self, h, ctx):
         """h: normed rows [R, hidden] -> float32 logits [R, vocab]."""

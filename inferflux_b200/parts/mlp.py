@@ -13,31 +13,35 @@ from .base import FeedForward, WeightBuffers, register_part
 
 @register_part("ffn", "swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size."""
+    """params: hidden_size, intermediate_size, names (tensor names of gate, up, down)."""
 
     takes_scaled_rows = True          # h goes only into the stacked projection
 
+    _NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        self.names = dict(self._NAMES)
+        self.names.update(spec.params.get("names") or {})
         self.w_gate_up = None
         self.w_down = None
 
     def param_specs(self):
+        n = self.names
         return {
-            "gate_proj.weight": TensorSpec((self.inter, self.hidden)),
-            "up_proj.weight": TensorSpec((self.inter, self.hidden)),
-            "down_proj.weight": TensorSpec((self.hidden, self.inter)),
+            n["gate"]: TensorSpec((self.inter, self.hidden)),
+            n["up"]: TensorSpec((self.inter, self.hidden)),
+            n["down"]: TensorSpec((self.hidden, self.inter)),
         }
 
     def load(self, tensors, dtype, device):
         self.buffers = buf = WeightBuffers(device, {"w_gate_up": ((2 * self.inter, self.hidden), dtype),
                                                     "w_down": ((self.hidden, self.inter), dtype)})
-        buf["w_gate_up"][:self.inter].copy_(tensors["gate_proj.weight"])
-        buf["w_gate_up"][self.inter:].copy_(tensors["up_proj.weight"])
-        buf["w_down"].copy_(tensors["down_proj.weight"])
+        buf["w_gate_up"][:self.inter].copy_(tensors[self.names["gate"]])
+        buf["w_gate_up"][self.inter:].copy_(tensors[self.names["up"]])
+        buf["w_down"].copy_(tensors[self.names["down"]])
         self.w_gate_up, self.w_down = buf["w_gate_up"], buf["w_down"]
 
     def forward(self, h, ctx):

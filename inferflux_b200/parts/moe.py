@@ -1,0 +1,82 @@
+"""A feed-forward made of many small experts of which every token uses a few.
+
+    z = W_router h (float32)      scores = softmax(z) over all router outputs
+    chosen = the `top` outputs with the largest scores + correction        (the correction only steers the choice)
+    y = sum over the chosen of score * expert(h)                           (scores as they are, not renormalised)
+
+An expert is W_down act(W_up h) with act = relu^2 and no biases.  The last `identity` router outputs have no
+weights: such an expert hands h on unchanged.  Expert weights are stacked at load, [experts, ff, width] and
+[experts, width, ff], so that the kernels find an expert by its number.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .base import FeedForward, WeightBuffers, register_part
+
+
+@register_part("ffn", "moe")
+class MixtureOfExperts(FeedForward):
+    """params: hidden_size, expert_size (ff of an expert), num_experts, num_identity (default 0), top,
+    activation (`relu2`), correction (whether a selection bias tensor exists; default True),
+    names (tensor names of router, correction, and the patterns `up` / `down` with {e} for the expert's number)."""
+
+    _NAMES = {"router": "router", "correction": "correction", "up": "e{e}.up", "down": "e{e}.down"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.ff = int(p["expert_size"])
+        self.experts = int(p["num_experts"])
+        self.identity = int(p.get("num_identity", 0))
+        self.top = int(p["top"])
+        self.activation = str(p.get("activation", "relu2"))
+        if self.activation != "relu2":
+            raise ValueError(f"moe: unknown activation {self.activation!r} (known: relu2)")
+        if self.experts < 0 or self.identity < 0 or self.experts + self.identity < 1:
+            raise ValueError("moe: there must be at least one expert")
+        if not 1 <= self.top <= self.experts + self.identity:
+            raise ValueError(f"moe: top {self.top} of {self.experts + self.identity} experts")
+        if self.experts + self.identity > 1024:
+            raise ValueError("moe: more than 1024 router outputs are beyond the kernel")
+        self.has_correction = bool(p.get("correction", True))
+        self.names = dict(self._NAMES)
+        self.names.update(p.get("names") or {})
+        self.w_router = self.correction = self.w_up = self.w_down = None
+
+    def param_specs(self):
+        n, outs = self.names, self.experts + self.identity
+        specs = {n["router"]: TensorSpec((outs, self.hidden))}
+        if self.has_correction:
+            specs[n["correction"]] = TensorSpec((outs,), init="zeros")
+        for e in range(self.experts):
+            specs[n["up"].format(e=e)] = TensorSpec((self.ff, self.hidden))
+            specs[n["down"].format(e=e)] = TensorSpec((self.hidden, self.ff))
+        return specs
+
+    def load(self, tensors, dtype, device):
+        n, outs = self.names, self.experts + self.identity
+        layout = {"router": ((outs, self.hidden), dtype), "correction": ((outs,), torch.float32)}
+        if self.experts:
+            layout["up"] = ((self.experts, self.ff, self.hidden), dtype)
+            layout["down"] = ((self.experts, self.hidden, self.ff), dtype)
+        self.buffers = buf = WeightBuffers(device, layout)
+        buf["router"].copy_(tensors[n["router"]])
+        if self.has_correction:
+            buf["correction"].copy_(tensors[n["correction"]])
+        else:
+            buf["correction"].zero_()
+        for e in range(self.experts):                    # each expert into its slice of the stack
+            buf["up"][e].copy_(tensors[n["up"].format(e=e)])
+            buf["down"][e].copy_(tensors[n["down"].format(e=e)])
+        self.w_router, self.correction = buf["router"], buf["correction"]
+        self.w_up = buf["up"] if self.experts else None
+        self.w_down = buf["down"] if self.experts else None
+
+    def forward(self, h, ctx):
+        k = ctx.kernels
+        z = k.linear(h, self.w_router, out_dtype=torch.float32)                   # [T, experts + identity]
+        ids, weights = k.moe_route(z, self.correction, self.top)
+        return k.moe_experts(h, self.w_up, self.w_down, ids, weights, self.experts, ctx.dtype)

@@ -4,6 +4,8 @@ cuda_kernels.cu:93-116).  The rotation itself runs inside the mixer's fused
 rotate-and-append kernel; this part owns the table and the pairing."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionEncoding, RotaryTable, register_part
@@ -12,7 +14,10 @@ from .base import PositionEncoding, RotaryTable, register_part
 @register_part("position", "rope")
 class RotaryEncoding(PositionEncoding):
     """params: theta, rotary_dim (even, at most the head size), pairing
-    (`split_half`: element i pairs with i + rotary_dim/2; `interleaved`: 2i with 2i+1)."""
+    (`split_half`: element i pairs with i + rotary_dim/2; `interleaved`: 2i with 2i+1), scaling (None, or
+    {factor, low, high, original}: a frequency whose wavelength is below original/high stays, one whose
+    wavelength is above original/low is divided by factor, and in between the two are blended linearly in
+    original/wavelength).  The table is worked out in double precision and kept in float32."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -24,12 +29,39 @@ class RotaryEncoding(PositionEncoding):
         if self.rotary_dim <= 0 or self.rotary_dim % 2:
             raise ValueError(f"rope: rotary_dim must be positive and even, got {self.rotary_dim}")
         self.interleaved = pairing == "interleaved"
+        scaling = spec.params.get("scaling")
+        self.scaling = None
+        if scaling:
+            self.scaling = {k: float(scaling[k]) for k in ("factor", "low", "high", "original")}
+            if not (self.scaling["factor"] > 0 and self.scaling["original"] > 0 and self.scaling["high"] > self.scaling["low"] >= 0):
+                raise ValueError(f"rope: bad frequency scaling {scaling!r}")
         self._table = None
+
+    def frequencies(self):
+        """The rotary_dim / 2 frequencies as Python floats (double precision)."""
+        out = []
+        for i in range(self.rotary_dim // 2):
+            f = self.theta ** (-2.0 * i / self.rotary_dim)
+            if self.scaling is not None:
+                sc = self.scaling
+                turns = sc["original"] * f / (2.0 * math.pi)          # original / wavelength
+                if turns > sc["high"]:
+                    pass
+                elif turns < sc["low"]:
+                    f = f / sc["factor"]
+                else:
+                    blend = (turns - sc["low"]) / (sc["high"] - sc["low"])
+                    f = (1.0 - blend) * f / sc["factor"] + blend * f
+            out.append(f)
+        return out
 
     def rotary(self, device):
         if self._table is None or self._table.inv_freq.device != torch.device(device):
-            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
-            inv_freq = (1.0 / (self.theta ** exponent)).to(torch.float32)
+            if self.scaling is None:
+                exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+                inv_freq = (1.0 / (self.theta ** exponent)).to(torch.float32)
+            else:
+                inv_freq = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32)
             self._table = RotaryTable(inv_freq.to(device).contiguous(), self.rotary_dim, self.interleaved)
         return self._table
 

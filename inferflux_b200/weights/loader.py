@@ -30,12 +30,24 @@ from .safetensors_io import open_model_shards
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """What a part expects of one tensor."""
+    """What a part expects of one tensor.  A size of -1 in `shape` is left to the file (the part reads it
+    from the tensor it is handed); `made_shape` is then what random-weights mode makes."""
     shape: Tuple[int, ...]
     init: str = "normal"        # how random-weights mode fills it: normal | ones | zeros
     optional: bool = False      # may be absent from the file (the part then does without it)
     ignored: bool = False       # may be present but is not used (e.g. lm_head.weight of a tied model)
     invent: bool = True         # an optional tensor: whether random-weights mode makes it up
+    made_shape: Optional[Tuple[int, ...]] = None
+
+    def fits(self, got) -> bool:
+        got = tuple(got)
+        return len(got) == len(self.shape) and all(w == -1 or int(g) == int(w) for g, w in zip(got, self.shape))
+
+    def shape_to_make(self) -> Tuple[int, ...]:
+        shape = tuple(self.made_shape) if self.made_shape is not None else tuple(self.shape)
+        if any(d < 0 for d in shape):
+            raise ValueError(f"a tensor of shape {self.shape} leaves a size to the file; random weights need `made_shape`")
+        return shape
 
 
 class WeightError(ValueError):
@@ -82,7 +94,7 @@ def check_tensors(found: Dict[str, Tuple[int, ...]], expected: Dict[str, TensorS
                       f"(the configuration ties it to another tensor)", stacklevel=3)
     unexpected = [n for n in found if n not in expected and not n.endswith(IGNORED_SUFFIXES)]
     wrong = [(n, tuple(found[n]), tuple(s.shape)) for n, s in expected.items()
-             if n in found and not s.ignored and tuple(found[n]) != tuple(s.shape)]
+             if n in found and not s.ignored and not s.fits(found[n])]
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where)
 

@@ -105,17 +105,17 @@ def random_tensors(expected: Dict[str, TensorSpec], seed: int, dtype=torch.bfloa
         if spec.ignored or (spec.optional and not spec.invent):
             continue
         if spec.init == "normal":
-            t = counter_normal(spec.shape, seed, name, 0.0, std, dtype, dev)
+            t = counter_normal(spec.shape_to_make(), seed, name, 0.0, std, dtype, dev)
         elif spec.init == "ones":
             if norm_jitter:
-                t = counter_normal(spec.shape, seed, name, 1.0, norm_jitter, dtype, dev)
+                t = counter_normal(spec.shape_to_make(), seed, name, 1.0, norm_jitter, dtype, dev)
             else:
-                t = torch.ones(spec.shape, dtype=dtype, device=dev)
+                t = torch.ones(spec.shape_to_make(), dtype=dtype, device=dev)
         elif spec.init == "zeros":
             if norm_jitter:
-                t = counter_normal(spec.shape, seed, name, 0.0, norm_jitter, dtype, dev)
+                t = counter_normal(spec.shape_to_make(), seed, name, 0.0, norm_jitter, dtype, dev)
             else:
-                t = torch.zeros(spec.shape, dtype=dtype, device=dev)
+                t = torch.zeros(spec.shape_to_make(), dtype=dtype, device=dev)
         else:
             raise ValueError(f"unknown init {spec.init!r} for {name}")
         out[name] = t

@@ -68,7 +68,11 @@ class PlainKernels:
         return value if bias is None else value + bias.to(value.dtype)
 
     # --------------------------------------------------------------- attention
-    def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
+    def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm=None, k_norm=None, norm_eps=0.0, dv=None,
+                    own_kv=True):
+        if q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv:
+            return self._norm_rope_append(qkv, rotary, nq, nkv, d, d if dv is None else dv, ctx, cache, q_norm, k_norm,
+                                          norm_eps, own_kv)
         T = qkv.shape[0]
         x = qkv.to(self.acc)
         if bias is not None:
@@ -98,9 +102,69 @@ class PlainKernels:
             cache.kv[page, 1, :, off, :] = x[:, nq + nkv:, :].to(cache.kv.dtype)
         return x[:, :nq, :].reshape(T, nq * d).contiguous()
 
-    def attention(self, q, nq, nkv, d, window, scale, ctx, cache):
+    def _turn(self, x, rotary, pos):
+        """x [T, heads, d]: the first rotary_dim elements of every head turned by position * inv_freq."""
+        if rotary is None:
+            return x
+        rot = rotary.rotary_dim
+        ang = pos.to(torch.float32)[:, None] * rotary.inv_freq[None, :].to(torch.float32)
+        cos, sin = torch.cos(ang).to(self.acc)[:, None, :], torch.sin(ang).to(self.acc)[:, None, :]
+        part = x[..., :rot]
+        if rotary.interleaved:
+            a, b = part[..., 0::2], part[..., 1::2]
+            turned = torch.stack([a * cos - b * sin, a * sin + b * cos], dim=-1).flatten(-2)
+        else:
+            a, b = part[..., :rot // 2], part[..., rot // 2:]
+            turned = torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
+        return torch.cat([turned, x[..., rot:]], dim=-1)
+
+    def _norm_rope_append(self, qkv, rotary, nq, nkv, d, dv, ctx, cache, q_norm, k_norm, norm_eps, own_kv):
+        T = qkv.shape[0]
+        x = qkv.to(self.acc)
+        pos = ctx.positions.long()
+
+        def head_norm(v, w):
+            if w is None:
+                return v
+            return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + norm_eps) * w.to(self.acc)
+        q = self._turn(head_norm(x[:, :nq * d].view(T, nq, d), q_norm), rotary, pos)
+        if own_kv:
+            k = self._turn(head_norm(x[:, nq * d:(nq + nkv) * d].view(T, nkv, d), k_norm), rotary, pos)
+            v = x[:, (nq + nkv) * d:].view(T, nkv, dv)
+            if cache.writes and cache.kv is not None:
+                P = cache.page_size
+                slot = ctx.req_slot.long()[ctx.token_req.long()]
+                page = cache.block_table[slot, pos // P].long()
+                off = pos % P
+                cache.kv[page, 0, :, off, :d] = k.to(cache.kv.dtype)
+                cache.kv[page, 1, :, off, :dv] = v.to(cache.kv.dtype)
+        return q.to(qkv.dtype).reshape(T, nq * d).contiguous()
+
+    def attention(self, q, nq, nkv, d, window, scale, ctx, cache, chunk=None, sink=False, dv=None):
+        dv = d if dv is None else dv
         T = q.shape[0]
         P = cache.page_size
+        if chunk or sink or dv != d:
+            out = torch.empty((T, nq, dv), dtype=q.dtype, device=q.device)
+            qv = q.view(T, nq, d).to(self.acc)
+            pos_all, req_all, slots = ctx.positions.tolist(), ctx.token_req.tolist(), ctx.req_slot.tolist()
+            for t in range(T):
+                pos, slot = pos_all[t], slots[req_all[t]]
+                first = max(0, pos - window + 1) if window else 0
+                if chunk:
+                    first = max(first, pos // chunk * chunk)
+                keys = torch.arange(first, pos + 1, device=q.device)
+                pages = cache.block_table[slot, keys // P].long()
+                K = cache.kv[pages, 0, :, keys % P, :d].to(self.acc)
+                V = cache.kv[pages, 1, :, keys % P, :dv].to(self.acc)
+                for h in range(nq):
+                    g = h // (nq // nkv)
+                    s = (K[:, g, :] @ qv[t, h]) * scale
+                    if sink:
+                        s = torch.cat([s, torch.zeros(1, dtype=s.dtype)])
+                    p = torch.softmax(s, dim=0)[:keys.numel()]
+                    out[t, h] = (p @ V[:, g, :]).to(q.dtype)
+            return out.reshape(T, nq * dv)
         out = torch.empty((T, nq, d), dtype=q.dtype, device=q.device)
         qv = q.view(T, nq, d).to(self.acc)
         pos_all = ctx.positions.tolist()
@@ -122,11 +186,11 @@ class PlainKernels:
         return out.reshape(T, nq * d)
 
     # ------------------------------------------- layers that norm a sublayer's output
-    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None):
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, cast_out=False):
         ya = y.to(self.acc)
         x += (ya * torch.rsqrt((ya * ya).mean(-1, keepdim=True) + eps_post) * w_post.to(self.acc)).to(torch.float32)
         if w_next is None:
-            return None
+            return x.to(out_dtype or y.dtype) if cast_out else None
         return self.rmsnorm(x, w_next, eps_next, out_dtype or y.dtype)
 
     def concat_cast(self, a, b, dtype):
@@ -157,6 +221,65 @@ class PlainKernels:
                 out[lo:hi] += wa[:, taps - 1 - k] * seq[taps - 1 - k:taps - 1 - k + (hi - lo)]
             state[slots[r], index] = seq[-(taps - 1):].to(state.dtype)
         return out.to(h.dtype)
+
+    # ------------------------------------------------- recurrence with matrix state
+    def cast_rows(self, x, dtype):
+        return x if dtype == torch.float32 else x.to(dtype)
+
+    def tanh(self, z):
+        z.copy_(torch.tanh(z.to(self.acc)))
+        return z
+
+    def token_shift_mix(self, x, mu, state, prev_offset, ctx, out_dtype):
+        T, C = x.shape
+        before = torch.empty_like(x)
+        before[1:] = x[:-1]
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
+        for r in range(ctx.num_requests):
+            before[cu[r]] = state[slots[r], prev_offset:prev_offset + C]
+        xa, ba = x.to(self.acc), before.to(self.acc)
+        return (xa[None] + (ba - xa)[None] * mu.to(self.acc)[:, None, :]).to(out_dtype)
+
+    def wkv_scan(self, r, k, v, w_raw, g, w0, u, norm_w, eps, heads, dim, state, prev_offset, x, ctx, out_dtype):
+        T = r.shape[0]
+        A = self.acc
+        shape = (T, heads, dim)
+        ra, ka, va = r.to(A).view(shape), k.to(A).view(shape), v.to(A).view(shape)
+        decay = torch.exp(-torch.exp(w_raw.to(A) + w0.to(A))).view(shape)
+        ua = u.to(A).view(heads, dim)
+        out = torch.empty(shape, dtype=A)
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
+        for q in range(ctx.num_requests):
+            S = state[slots[q], :prev_offset].to(A).view(heads, dim, dim).clone()
+            for t in range(cu[q], cu[q + 1]):
+                kv = ka[t][:, :, None] * va[t][:, None, :]
+                out[t] = torch.einsum("hij,hi->hj", S + ua[:, :, None] * kv, ra[t])
+                S = decay[t][:, :, None] * S + kv
+            state[slots[q], :prev_offset] = S.reshape(-1).to(state.dtype)
+            state[slots[q], prev_offset:] = x[cu[q + 1] - 1]
+        out = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
+        ga = g.to(A)
+        y = out.reshape(T, heads * dim) * norm_w.to(A) * (ga / (1.0 + torch.exp(-ga)))
+        return y.to(out_dtype)
+
+    # ------------------------------------------------------- mixture of experts
+    def moe_route(self, z, correction, top):
+        s = torch.softmax(z.to(self.acc), dim=-1)
+        choice = s if correction is None else s + correction.to(self.acc)
+        ids = torch.topk(choice, top, dim=-1).indices
+        return ids.to(torch.int32), torch.gather(s, 1, ids).to(torch.float32)
+
+    def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype):
+        ha = h.to(self.acc)
+        out = torch.zeros_like(ha)
+        for t in range(h.shape[0]):
+            for e, wgt in zip(ids[t].tolist(), weights[t].to(self.acc)):
+                if e >= experts:
+                    out[t] += wgt * ha[t]
+                else:
+                    a = torch.relu(w_up[e].to(self.acc) @ ha[t]) ** 2
+                    out[t] += wgt * (w_down[e].to(self.acc) @ a.to(h.dtype).to(self.acc))
+        return out.to(out_dtype)
 
     # -------------------------------------------------------- latent attention
     def latent_norm_append(self, rows, col0, rank, w, eps, ctx, cache):
