@@ -642,6 +642,203 @@ def run_design(args, pk):
     return 0
 
 
+# ---------------------------------------------------------------- Zeluzen beside the closest existing model
+# Layers in the pattern recurrence, recurrence, attention, recurrence, recurrence, attention that reads the cache of the
+# attention layer before it; feed-forwards alternate between the gated one of the Qwen2 shape and a mixture of 16 + 2
+# experts of which a token uses 4, sized so that a token's active feed-forward parameters equal the gated one's.
+def zeluzen_config(shape, layers=0, chunk=8192):
+    from inferflux_b200.config import ZeluzenConfig
+    s = DESIGN_SHAPES[shape]
+    q = qwen7b_config(s["qwen"])
+    w, inter = s["width"], q.intermediate_size
+    n = layers or q.num_hidden_layers
+    dense = {"kind": "dense", "ff": inter}
+    moe = {"kind": "moe", "expert": {"ff": (3 * inter // 8) // 64 * 64}, "router": {"experts": 16, "identity": 2, "top": 4}}
+    rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    out, last_attention = [], None
+    for i in range(n):
+        mlp = dense if i % 2 == 0 else moe
+        if i % 3 != 2:
+            out.append({"type": "wkv", "mixer": {"heads": w // 64, "dim": 64, "rank": 64}, "mlp": mlp})
+            continue
+        mixer = {"heads": s["heads"], "kv_heads": q.num_key_value_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "mask": {"size": chunk}, "rot": rot}
+        if last_attention is not None and (i // 3) % 2 == 1:
+            mixer["kv_from"] = last_attention
+        else:
+            last_attention = i
+        out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return ZeluzenConfig.from_dict({"architecture": "Zeluzen", "vocab": s["vocab"], "width": w, "norm": {"eps": 1e-6}, "layers": out})
+
+
+def zeluzen_costs(cfg, batch, context, tokens):
+    """(bytes a decode step must read or write, FLOPs of a prefill of `tokens`): matrices (a token's 4 experts, and at
+    most all of them), recurrent state in and out, cached keys and values."""
+    w, step_bytes, flops = cfg.width, 0, 0
+    for layer in cfg.layers:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if layer["type"] == "wkv":
+            hd, rank = m["heads"] * m["dim"], m.get("rank") or 16
+            params = 5 * hd * w + 2 * rank * max(w, hd)
+            step_bytes += 2 * batch * m["heads"] * m["dim"] * m["dim"] * 4
+            flops += 4 * tokens * hd * m["dim"]
+        else:
+            own = m.get("kv_from") is None
+            params = w * m["heads"] * m["dim"] + m["heads"] * m["vdim"] * w + (w * m["kv_heads"] * (m["dim"] + m["vdim"]) if own else 0)
+            keys = min(context, m["mask"]["size"]) if m.get("mask") else context
+            step_bytes += batch * keys * m["kv_heads"] * (m["dim"] + m["vdim"]) * 2
+            flops += 2 * m["heads"] * (m["dim"] + m["vdim"]) * (tokens * (tokens + 1) // 2)
+        step_bytes += 2 * params
+        flops += 2 * tokens * params
+        if mlp and mlp["kind"] == "dense":
+            step_bytes += 2 * 3 * w * mlp["ff"]
+            flops += 2 * tokens * 3 * w * mlp["ff"]
+        elif mlp:
+            r = mlp["router"]
+            step_bytes += 2 * 2 * w * mlp["expert"]["ff"] * min(r["experts"], batch * r["top"])
+            flops += 2 * tokens * 2 * w * mlp["expert"]["ff"] * r["top"]
+    return step_bytes + 2 * cfg.vocab * w, flops + 2 * cfg.vocab * w
+
+
+def zeluzen_kernels(kernels, zcfg, qcfg, pk, batch, context, tokens):
+    """The new design's kernels beside the like kernels of the closest model, each alone at the layer's sizes."""
+    import torch
+    from inferflux_b200.cache import CacheManager
+    from inferflux_b200.config import ScheduleEntry
+    from inferflux_b200.engine.batch import StepContext, StepEntry
+    from inferflux_b200.parts import KVCacheSpec
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    wk = next(l for l in zcfg.layers if l["type"] == "wkv")["mixer"]
+    at = next(l for l in zcfg.layers if l["type"] == "attention")["mixer"]
+    moe = next(l["mlp"] for l in zcfg.layers if l["mlp"] and l["mlp"]["kind"] == "moe")
+    w, H, D = zcfg.width, wk["heads"], wk["dim"]
+    nq, nkv, d = qcfg.num_attention_heads, qcfg.num_key_value_heads, qcfg.head_dim
+    page, out = 16, {}
+
+    def row(name, ms, bytes_=0, flops=0):
+        roof = max(bytes_ / hbm, flops / tf)
+        out[name] = {"us": round(ms * 1000, 1), "roofline_us": round(roof * 1e6, 1), "frac": round(roof / (ms * 1e-3), 3),
+                     "bound": "hbm" if bytes_ / hbm >= flops / tf else "tensor"}
+
+    def ctx_for(cache, spans):
+        entries, starts, slots = [], [], []
+        for rid, n in spans:
+            if rid not in cache:
+                cache.add_request(rid)
+            start = cache.length(rid)
+            cache.reserve(rid, start + n)
+            entries.append(StepEntry(rid, [0] * n, []))
+            starts.append(start)
+            slots.append(cache.slot(rid))
+        ctx = StepContext.build(kernels, bf, dev, entries, starts, slots, cache.drain_table_updates())
+        for g, (idx, pg) in zip(cache.groups, ctx.table_updates):
+            kernels.scatter_i32(g.table, idx, pg)
+        for (rid, n), start in zip(spans, starts):
+            cache.commit(rid, start + n)
+        return ctx
+
+    for what, spans_a, spans_b in (("decode", [(f"r{i}", context - 1) for i in range(batch)], [(f"r{i}", 1) for i in range(batch)]),
+                                   ("prefill", [], [("p", tokens)])):
+        T = sum(n for _r, n in spans_b)
+        keys = sum((context if what == "decode" else (n * (n + 1)) // 2) for _r, n in spans_b)
+        pages = (batch * context if what == "decode" else tokens) // page + 2 * batch + 2
+        cached = batch * context if what == "decode" else tokens
+        for name, spec, kw in (("attention with chunks and a sink", KVCacheSpec(at["kv_heads"], 128, None, chunk=at["mask"]["size"]),
+                                dict(chunk=at["mask"]["size"], sink=True, dv=128)),
+                               ("attention of the closest model", KVCacheSpec(nkv, d, None), {})):
+            cache = CacheManager([(spec, None)], page_size=page, num_pages=pages, max_seqs=batch,
+                                 max_seq_len=max(context, tokens) + 16, dtype=bf, device=dev)
+            cache.groups[0].pool.normal_()
+            if spans_a:
+                ctx_for(cache, spans_a)
+            ctx = ctx_for(cache, spans_b)
+            view = cache.view(ScheduleEntry(0, 0))
+            heads, kvh, hd = (at["heads"], at["kv_heads"], 128) if kw else (nq, nkv, d)
+            q = torch.randn(T, heads * hd, device=dev).to(bf)
+            ms = _event_times(lambda: kernels.attention(q, heads, kvh, hd, None, hd ** -0.5, ctx, view, **kw))
+            row(f"{name}, {what}", ms, bytes_=cached * 2 * kvh * hd * 2 + 4 * T * heads * hd, flops=4 * heads * hd * keys)
+            del cache
+        # the recurrence: state in and out, five float32 inputs, a scratch row and the output
+        state = torch.zeros(batch, H * D * D + w, device=dev)
+        ins = [torch.randn(T, H * D, device=dev) * 0.1 for _ in range(5)]
+        consts = [torch.zeros(H * D, device=dev), torch.zeros(H * D, device=dev), torch.ones(H * D, device=dev)]
+        x = torch.randn(T, w, device=dev)
+        ms = _event_times(lambda: kernels.wkv_scan(*ins, *consts, 1e-6, H, D, state, H * D * D, x, ctx, bf))
+        row(f"recurrence over {T} tokens ({what})", ms, bytes_=2 * len(spans_b) * H * D * D * 4 + T * H * D * (5 * 4 + 8 + 2),
+            flops=0)
+        mu = torch.rand(5, w, device=dev)
+        ms = _event_times(lambda: kernels.token_shift_mix(x, mu, state, H * D * D, ctx, bf))
+        row(f"five mixes of a token and the one before, {T} rows", ms, bytes_=T * w * (4 + 5 * 2))
+        y = torch.randn(T, w, device=dev).to(bf)
+        wn = torch.ones(w, device=dev)
+        ms = _event_times(lambda: kernels.postnorm_add(x, y, wn, 1e-6, out_dtype=bf, cast_out=True))
+        row(f"sum of the normed delta + rows in bfloat16, {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        ms = _event_times(lambda: kernels.add_rmsnorm(x, y, wn, 1e-6, bf))
+        row(f"sum + norm of the closest model, {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        # the experts against the closest model's gated feed-forward (both: all matrices a token uses)
+        E, top, ff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]
+        up = (torch.randn(E, ff, w, device=dev) * 0.02).to(bf)
+        down = (torch.randn(E, w, ff, device=dev) * 0.02).to(bf)
+        h = torch.randn(T, w, device=dev).to(bf)
+        z = torch.randn(T, E + moe["router"]["identity"], device=dev)
+        corr = torch.zeros(E + moe["router"]["identity"], device=dev)
+        ids, wts = kernels.moe_route(z, corr, top)
+        ms = _event_times(lambda: kernels.moe_route(z, corr, top))
+        row(f"router, {T} rows", ms, bytes_=T * (E + 2) * 4)
+        used = min(E, T * top)
+        ms = _event_times(lambda: kernels.moe_experts(h, up, down, ids, wts, E, bf))
+        row(f"experts, {T} rows", ms, bytes_=used * 2 * ff * w * 2, flops=2 * T * top * 2 * ff * w)
+        inter = qcfg.intermediate_size
+        wgu, wd = (torch.randn(2 * inter, w, device=dev) * 0.02).to(bf), (torch.randn(w, inter, device=dev) * 0.02).to(bf)
+        ms = _event_times(lambda: kernels.materialize(kernels.linear(kernels.linear_swiglu(h, wgu), wd, allow_partial=True)))
+        row(f"gated feed-forward of the closest model, {T} rows", ms, bytes_=3 * inter * w * 2, flops=2 * T * 3 * inter * w)
+        del up, down, wgu, wd
+    kernels.check_errors()
+    return out
+
+
+def run_design_zeluzen(args, pk):
+    """`--design zeluzen`: decode and prefill throughput of the design at real layer sizes beside the Qwen2 shape of
+    equal width, layer count and vocabulary, and its kernels beside the like kernels, one JSON line."""
+    import torch
+    page, batch, context = 16, args.batch, min(args.context, 4096)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    result = {"metric": "decode and prefill tokens/s of another design beside the closest model at equal size",
+              "design": args.design, "dtype": "bf16", "n_gpus": 1, "data": "synthetic: random weights, uniform random token ids",
+              "batch": batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "peaks": pk["source"], "shapes": {}}
+    kernels_table = None
+    for shape in ([args.shape] if args.shape in DESIGN_SHAPES else sorted(DESIGN_SHAPES)):
+        entry = {}
+        for name in ("zeluzen", "qwen2"):
+            cfg = zeluzen_config(shape, args.layers) if name == "zeluzen" else qwen7b_config(DESIGN_SHAPES[shape]["qwen"])
+            if args.layers and name == "qwen2":
+                cfg.num_hidden_layers = args.layers
+            longest = context + 4 * (warmup + 3 * steps) + 16 + batch
+            engine = _engine(cfg, page, batch, longest)
+            r = time_decode(engine, cfg, batch, steps, warmup, repeats=3, context=context, e2e=False)
+            pre_ms = time_prefill(engine, cfg, PREFILL_TOKENS, warmup=2, reps=5)
+            if name == "zeluzen":
+                step_bytes, flops = zeluzen_costs(cfg, batch, r["ctx"], PREFILL_TOKENS)
+            else:
+                step_bytes = weight_bytes(cfg, batch) + batch * r["ctx"] * kv_bytes_per_token(cfg)
+                flops = prefill_flops(cfg, PREFILL_TOKENS)
+            entry[name] = {"decode_tok_s": round(batch * 1000.0 / r["dev_ms"], 1), "decode_ms_per_step": round(r["dev_ms"], 3),
+                           "decode_hbm_frac": round(step_bytes / (r["dev_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 3),
+                           "launches_per_step": round(r["launches"], 1),
+                           "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 2),
+                           "prefill_tensor_frac": round(flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 3)}
+            if name == "zeluzen" and kernels_table is None:
+                kernels_table = zeluzen_kernels(engine.kernels, cfg, qwen7b_config(DESIGN_SHAPES[shape]["qwen"]), pk, batch,
+                                                context, PREFILL_TOKENS)
+                entry["kernels"] = kernels_table
+            del engine
+            torch.cuda.empty_cache()
+        result["shapes"][shape] = entry
+    print(json.dumps(result))
+    return 0
+
+
 def _engine(cfg, page, slots, longest, pages=None, chunk=2048):
     import torch
     from inferflux_b200 import Engine
@@ -675,7 +872,7 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true", help="skip the PyTorch baseline and the 1.5B-shape points")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the 2,048-token prefill and print a short line (for profiling prefill)")
-    ap.add_argument("--design", default="", choices=["", "dafolorn"],
+    ap.add_argument("--design", default="", choices=["", "dafolorn", "zeluzen"],
                     help="instead of the headline numbers: this design at real layer sizes beside the Qwen2 shape of equal "
                          "size (decode and prefill tokens/s, and its kernels beside the like kernels); --shape picks one size")
     args = ap.parse_args()
@@ -683,6 +880,8 @@ def main() -> int:
     pk = peaks()
     if args.impl == "reference":
         return run_reference(args, pk)
+    if args.design == "zeluzen":
+        return run_design_zeluzen(args, pk)
     if args.design:
         return run_design(args, pk)
     if args.gpus != 1:

@@ -35,6 +35,20 @@
 
 namespace ifx {
 
+// Which keys a query sees besides "not later than itself": the last `window` of them (> 0), only those of its own
+// stretch of `chunk` positions (> 0), or both; `sink`: the softmax's denominator holds one more unit, a key of score 0
+// that brings no value.
+struct KeyMask {
+  int window, chunk, sink;
+  __device__ __forceinline__ int first(int pos) const {          // the first key the query at `pos` sees
+    int f = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) f = max(f, pos / chunk * chunk);
+    return f;
+  }
+  __device__ __forceinline__ bool any() const { return window > 0 || chunk > 0; }
+};
+
+
 namespace cg = cooperative_groups;
 typedef __nv_bfloat16 bf16;
 
@@ -102,7 +116,7 @@ template <int D, int KT>
 __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
                     const int* __restrict__ tiles, const int* __restrict__ req_slot, bf16* __restrict__ out, int nq,
-                    int nkv, int page_size, int page_shift, int max_blocks, int num_pages, int window,
+                    int nkv, int page_size, int page_shift, int max_blocks, int num_pages, KeyMask window,
                     float scale_log2, int tbl_cap) {
   constexpr int LDS = D + 8;            // shared-memory row stride in elements
   constexpr int CPR = D / 8;            // 16-byte chunks per row
@@ -122,7 +136,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   PageMap pm{table_g, 0, page_size, page_shift, num_pages, nkv, h / (nq / nkv)};
   const size_t v_off = (size_t)nkv * page_size * D;
 
-  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kfirst = window.first(pos0);
   const int kend = pos0 + rows;
   const int tile_begin = kfirst / KT, tile_end = (kend + KT - 1) / KT;
   {   // the block-table entries of keys [kfirst, kend) go to shared memory once
@@ -168,7 +182,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
   const int p_lo = pos0 + warp * 16 + (lane >> 2), p_hi = p_lo + 8;
-  const int w_lo = window > 0 ? p_lo - window + 1 : 0, w_hi = window > 0 ? p_hi - window + 1 : 0;
+  const int w_lo = window.first(p_lo), w_hi = window.first(p_hi);
 
   for (int t = tile_begin; t < tile_end; ++t) {
     const int stage = (t - tile_begin) & 1;
@@ -203,7 +217,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
     // wholly inside every row's range (most tiles of a long prompt) skips the compares.
     const int key0 = t * KT;
     const bool inside = key0 + KT - 1 <= pos0 + warp * 16 && key0 >= kfirst &&
-                        (window <= 0 || key0 >= pos0 + warp * 16 + 15 - window + 1);
+                        (!window.any() || key0 >= window.first(pos0 + warp * 16 + 15));
     if (!inside) {
 #pragma unroll
       for (int n = 0; n < KT / 8; ++n) {
@@ -268,6 +282,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if (window.sink) {                                    // the sink's share, relative to the row's maximum
+    l_lo += exp2f(-m_lo * scale_log2);
+    l_hi += exp2f(-m_hi * scale_log2);
+  }
   const float i_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, i_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
   const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
 #pragma unroll
@@ -287,7 +305,7 @@ template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
                    const int4* __restrict__ decode_meta, bf16* __restrict__ out, int nq, int nkv, int page_size,
-                   int page_shift, int max_blocks, int num_pages, int window, float scale_log2, int tbl_cap) {
+                   int page_shift, int max_blocks, int num_pages, KeyMask window, float scale_log2, int tbl_cap) {
   constexpr int LDS = D + 8;
   constexpr int CPR = D / 8;
   constexpr int STAGE_ELEMS = 2 * 16 * LDS;             // K tile then V tile
@@ -314,7 +332,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
   PageMap pm{table_g, 0, page_size, page_shift, num_pages, nkv, g};
   const size_t v_off = (size_t)nkv * page_size * D;
 
-  const int kfirst = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kfirst = window.first(pos);
   const int kend = pos + 1;
   const int per_split = (((kend - kfirst + num_splits - 1) / num_splits) + 63) / 64 * 64;
   const int k0 = kfirst + split * per_split;
@@ -489,6 +507,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
     }
     const int head = g * G + row;
     if (num_splits == 1) {
+      if (window.sink && M != -INFINITY) L += exp2f(-M);
       out[((size_t)t * nq + head) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
     } else {
       fin_o[row * D + dim] = O;
@@ -530,6 +549,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
         L += f * ls[c];
       }
     }
+    if (window.sink && M != -INFINITY) L += exp2f(-M);
     out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
   }
   cluster.sync();                                       // nobody leaves while its shared memory is being read
@@ -549,7 +569,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16* __restrict__ q,
                        const int* __restrict__ block_table, const int4* __restrict__ decode_meta,
                        bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                       int num_pages, int window, float scale_log2, int tbl_cap, int* __restrict__ error_flag) {
+                       int num_pages, KeyMask window, float scale_log2, int tbl_cap, int* __restrict__ error_flag) {
   constexpr int LDS = D + 8;
   constexpr int CPR = D / 8;
   constexpr int HALVES = D / 64;
@@ -587,7 +607,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   const int* table = table_g;
   int blk_base = 0;
 
-  const int kfirst = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kfirst = window.first(pos);
   const int kstart = kfirst & ~15;                      // tiles start on multiples of 16 so that one lies in one page
   const int kend = pos + 1;
   const int per_split = (((kend - kstart + num_splits - 1) / num_splits) + WARPS * 16 - 1) / (WARPS * 16) * (WARPS * 16);
@@ -786,7 +806,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       }
     }
     if (num_splits == 1) {
-      out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+      if (window.sink && M != -INFINITY) L += exp2f(-M);
+    out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
     } else {
       fin_o[row * D + dim] = O;
       if (dim == 0) {
@@ -825,6 +846,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
         L += f * ls[c];
       }
     }
+    if (window.sink && M != -INFINITY) L += exp2f(-M);
     out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
   }
   cluster.sync();
@@ -833,7 +855,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
 template <int D, int STAGES, int WARPS>
 int launch_decode_tma_stages(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
                              bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                             int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
+                             int num_pages, KeyMask window, float scale_log2, int num_splits, int max_keys, int* error_flag,
                              cudaStream_t stream) {
   constexpr int stage_bytes = WARPS * STAGES * 2 * 16 * D * 2;
   constexpr int merge_bytes = (WARPS * 16 * D + 2 * WARPS * 16) * 4;
@@ -874,7 +896,7 @@ int launch_decode_tma_stages(const CUtensorMap& pool_map, const bf16* q, const i
 template <int D>
 int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
                       bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                      int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
+                      int num_pages, KeyMask window, float scale_log2, int num_splits, int max_keys, int* error_flag,
                       cudaStream_t stream) {
   constexpr int STAGES = D <= 128 ? 3 : 2;
   const long long blocks = (long long)num_items * nkv * num_splits;
@@ -889,7 +911,7 @@ int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* blo
 template <int D>
 int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, const int* tiles, const int* req_slot,
                    bf16* out, int num_tiles, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                   int num_pages, int window, float scale_log2, int max_keys, cudaStream_t stream) {
+                   int num_pages, KeyMask window, float scale_log2, int max_keys, cudaStream_t stream) {
   constexpr int KT = 64;                                // keys per tile
   constexpr int tile_bytes = (64 + 4 * KT) * (D + 8) * 2;
   int tbl_cap = max_keys / page_size + 2;               // entries a tile can need
@@ -911,7 +933,7 @@ int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, c
 template <int D>
 int launch_decode(const bf16* q, const bf16* kv_pool, const int* block_table, const int4* decode_meta, bf16* out,
                   int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks, int num_pages,
-                  int window, float scale_log2, int num_splits, int max_keys, cudaStream_t stream) {
+                  KeyMask window, float scale_log2, int num_splits, int max_keys, cudaStream_t stream) {
   constexpr int STAGES = D <= 128 ? 3 : 2;
   constexpr int stage_bytes = 4 * STAGES * 2 * 16 * (D + 8) * 2;
   constexpr int merge_bytes = (4 * 16 * D + 2 * 4 * 16) * 4;
@@ -980,10 +1002,12 @@ int ifx_attention_mma_supports(int d) {
 
 // tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 256, first position).
 // max_keys: no request of the step holds more keys than this (sizes the shared-memory copy of the block table).
-int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
-                               const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
-                               int max_blocks, int num_pages, int window, float scale, int max_keys, int* error_flag,
-                               cudaStream_t stream) {
+// chunk, sink: see KeyMask.
+int ifx_attention_prefill_bf16_ex(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
+                                  const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
+                                  int max_blocks, int num_pages, int window_size, int chunk, int sink, float scale,
+                                  int max_keys, int* error_flag, cudaStream_t stream) {
+  const KeyMask window{window_size, chunk, sink};
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535 || !(scale > 0.0f))
     return IFX_E_BADARG;                                  // the kernels take the maximum before scaling
@@ -994,6 +1018,14 @@ int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* bl
                      nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, max_keys, stream)
   IFX_DISPATCH_D(d, CALL)
 #undef CALL
+}
+
+int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
+                               const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
+                               int max_blocks, int num_pages, int window, float scale, int max_keys, int* error_flag,
+                               cudaStream_t stream) {
+  return ifx_attention_prefill_bf16_ex(q, kv_pool, block_table, tiles, req_slot, out, num_tiles, nq, nkv, d, page_size,
+                                       max_blocks, num_pages, window, 0, 0, scale, max_keys, error_flag, stream);
 }
 
 // The largest cluster (blocks that share one token's keys) the decode kernel takes for this head and page size.
@@ -1007,10 +1039,11 @@ int ifx_attention_decode_max_splits(int d, int page_size) {
 // num_splits: 1, 2, 4 or 8 blocks (one cluster) share a token's key range; it must divide d.  16 where
 // ifx_attention_decode_max_splits says so (the TMA variant, a cluster size beyond the portable 8).
 // max_keys: no token of the step sees more keys than this.
-int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
-                              void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
-                              int num_pages, int window, float scale, int num_splits, int max_keys, int* error_flag,
-                              cudaStream_t stream) {
+int ifx_attention_decode_bf16_ex(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
+                                 void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
+                                 int num_pages, int window_size, int chunk, int sink, float scale, int num_splits,
+                                 int max_keys, int* error_flag, cudaStream_t stream) {
+  const KeyMask window{window_size, chunk, sink};
   if (num_items <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || nkv > 65535 ||
       nq > 65535)
@@ -1041,6 +1074,14 @@ int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* blo
                     max_keys, stream)
   IFX_DISPATCH_D(d, CALL)
 #undef CALL
+}
+
+int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
+                              void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
+                              int num_pages, int window, float scale, int num_splits, int max_keys, int* error_flag,
+                              cudaStream_t stream) {
+  return ifx_attention_decode_bf16_ex(q, kv_pool, block_table, decode_meta, out, num_items, nq, nkv, d, page_size,
+                                      max_blocks, num_pages, window, 0, 0, scale, num_splits, max_keys, error_flag, stream);
 }
 
 }  // extern "C"

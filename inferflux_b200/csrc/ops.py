@@ -145,7 +145,8 @@ class CudaKernels:
                    "ifx_short_conv", "ifx_latent_norm_append", "ifx_latent_attention_generic", "ifx_latent_attention_mma",
                    "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched", "ifx_gemm_skinny_act",
                    "ifx_attention_generic_ex", "ifx_norm_rope_append", "ifx_token_shift_mix", "ifx_cast_rows",
-                   "ifx_wkv_scan", "ifx_moe_route", "ifx_moe_experts", "ifx_tanh_rows"):
+                   "ifx_wkv_scan", "ifx_moe_route", "ifx_moe_experts", "ifx_tanh_rows",
+                   "ifx_attention_prefill_bf16_ex", "ifx_attention_decode_bf16_ex"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
@@ -769,6 +770,35 @@ class CudaKernels:
         _need(kv.shape[1] == 2 and kv.shape[2] == nkv and d_row >= max(d, dv) and d_row % 8 == 0 and d_row <= 256,
               "attention: the cache does not fit the heads")
         out = torch.empty((T, nq * dv), dtype=q.dtype, device=q.device)
+        win = 0 if window is None else int(window)
+        if (q.dtype == torch.bfloat16 and d == dv == d_row and nq // nkv <= 16 and self.lib.ifx_attention_mma_supports(d)
+                and os.environ.get("INFERFLUX_B200_MASKED_TILES", "1") != "0"):
+            # the tiled kernels: prompt portions on mma.sync tiles, single tokens on the cluster kernel
+            if "attn.prefill_tiles" not in ctx.extra:          # a step context built without the mixer as a provider
+                for name, vals in self.attention_sections(ctx).items():
+                    ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=q.device)
+                    ctx.extra_len[name] = len(vals)
+            num_tiles = ctx.extra_len["attn.prefill_tiles"] // 4
+            common = (cache.page_size, table.shape[1], kv.shape[0], win, int(chunk or 0), int(bool(sink)), ctypes.c_float(scale))
+            if num_tiles:
+                _check(self.lib.ifx_attention_prefill_bf16_ex(
+                    _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.prefill_tiles"]), _ptr(ctx.req_slot), _ptr(out),
+                    num_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),
+                    "attention (masked, prompt portions)")
+                self.launches += 1
+            n = ctx.extra_len["attn.decode_rows"]
+            if n:
+                max_keys = int(ctx.max_kv_len)
+                if win:
+                    max_keys = min(max_keys, win)
+                if chunk:
+                    max_keys = min(max_keys, int(chunk))
+                splits = self.decode_splits(n, nkv, max_keys, int(self.lib.ifx_attention_decode_max_splits(d, cache.page_size)))
+                _check(self.lib.ifx_attention_decode_bf16_ex(
+                    _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.decode_meta"]), _ptr(out), n, nq, nkv, d, *common,
+                    splits, max_keys, _ptr(self.error_flag), _stream()), "attention (masked, decoded tokens)")
+                self.launches += 1
+            return out
         _check(self.lib.ifx_attention_generic_ex(
             _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(None),
             _ptr(out), T, nq, nkv, d, dv, d_row, cache.page_size, table.shape[1], kv.shape[0],

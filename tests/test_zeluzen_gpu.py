@@ -208,7 +208,7 @@ def test_normed_heads_rotation_and_cache_write(cuda_kernels, dtype, tol, sizes):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("chunk", [None, 1, 7, 16, 24, 300])
-@pytest.mark.parametrize("sizes", [(4, 2, 16, 24, 8), (2, 2, 64, 64, 16), (6, 1, 8, 40, 16)])
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 24, 8), (2, 2, 64, 64, 16), (6, 1, 8, 40, 16), (4, 2, 32, 32, 8), (8, 2, 128, 128, 16)])
 def test_attention_with_chunks_and_sink_planted_keys(cuda_kernels, dtype, tol, chunk, sizes):
     """One key is made to stand out for one query at a time: far back, at a page border, just inside and just outside
     the query's chunk, in a prompt portion and in a token decoded alone.  The output must be that key's value when
@@ -268,6 +268,57 @@ def test_attention_with_chunks_and_sink_planted_keys(cuda_kernels, dtype, tol, c
     ctx, cache = _Ctx([(5, 1)], [2], DEV), _Cache(kv.to(DEV), table.to(DEV), page)
     with_sink = cuda_kernels.attention(q.to(DEV), nq, nkv, d, None, 25.0, ctx, cache, chunk=1, sink=True, dv=dv)
     assert float(with_sink.float().abs().max()) < 1e-2 * float(V[5].float().abs().max())
+
+
+@pytest.mark.parametrize("chunk", [None, 1024, 300, 64])
+@pytest.mark.parametrize("sizes", [(8, 2, 128, 16), (4, 4, 64, 16), (6, 2, 32, 8), (16, 1, 96, 32)])
+def test_masked_attention_tiles_against_the_per_token_kernel(cuda_kernels, chunk, sizes, monkeypatch):
+    """bfloat16: three requests with 1,500, 700 and 40 cached keys; a step that decodes one token of the first two and
+    brings a portion of 300 of a fourth, and a step of single tokens only (the key range cut over a cluster)."""
+    from inferflux_b200.cache import CacheManager
+    from inferflux_b200.config import ScheduleEntry
+    from inferflux_b200.engine.batch import StepContext, StepEntry
+    from inferflux_b200.parts import KVCacheSpec
+    nq, nkv, d, page = sizes
+    bf = torch.bfloat16
+    cache = CacheManager([(KVCacheSpec(nkv, d, None), None)], page_size=page, num_pages=3000 // page + 8, max_seqs=4,
+                         max_seq_len=2048, dtype=bf, device=DEV)
+    cache.groups[0].pool.normal_()
+    cache.groups[0].pool[:, :, 0] *= 0.3                                     # keys: scores that are no flat softmax
+
+    def step(spans):
+        entries, starts, slots = [], [], []
+        for rid, n in spans:
+            if rid not in cache:
+                cache.add_request(rid)
+            start = cache.length(rid)
+            cache.reserve(rid, start + n)
+            entries.append(StepEntry(rid, [0] * n, []))
+            starts.append(start)
+            slots.append(cache.slot(rid))
+        ctx = StepContext.build(cuda_kernels, bf, DEV, entries, starts, slots, cache.drain_table_updates())
+        for g, (idx, pg) in zip(cache.groups, ctx.table_updates):
+            cuda_kernels.scatter_i32(g.table, idx, pg)
+        for (rid, n), start in zip(spans, starts):
+            cache.commit(rid, start + n)
+        return ctx
+    step([("a", 1499), ("b", 699), ("c", 39)])
+    view = cache.view(ScheduleEntry(0, 0))
+    for spans in ([("a", 1), ("b", 1), ("d", 300)], [("a", 1), ("b", 1), ("c", 1)]):
+        ctx = step(spans)
+        T = ctx.num_tokens
+        q = _rnd(T, nq * d, seed=T).to(bf).to(DEV)
+        outs = []
+        for tiles in ("1", "0"):
+            monkeypatch.setenv("INFERFLUX_B200_MASKED_TILES", tiles)
+            launches = cuda_kernels.launches
+            outs.append(cuda_kernels.attention(q, nq, nkv, d, None, d ** -0.5, ctx, view, chunk=chunk, sink=True).float())
+            assert cuda_kernels.launches - launches == (1 if tiles == "0" else len({n == 1 for _r, n in spans}))
+        cuda_kernels.check_errors()
+        assert float((outs[0] - outs[1]).abs().max()) < 2e-2, (spans, float((outs[0] - outs[1]).abs().max()))
+        # without the sink the weights sum to one: the outputs are larger
+        plain = cuda_kernels.attention(q, nq, nkv, d, None, d ** -0.5, ctx, view, chunk=chunk or 4096, sink=False).float()
+        assert float(plain.abs().mean()) > float(outs[0].abs().mean())
 
 
 def test_postnorm_add_hands_on_the_rows_themselves(cuda_kernels):
