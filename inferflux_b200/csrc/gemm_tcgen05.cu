@@ -6,6 +6,10 @@
 //   SWIGLU   W holds N gate rows and, `up_row_offset` rows further, N up rows;
 //            out[m, n] = silu(acc_gate) * acc_up               (bfloat16; no [M, 2N] round trip,
 //                                                               no separate activation kernel)
+//   GROUP_RELU2  rows are sorted into groups of whole 128-row tiles; tile mt multiplies with the weight rows
+//            [tile_group[mt] * group_rows, + N) of a stack of matrices (a negative entry: the tile is unused and
+//            skipped);  out[m, n] = relu(acc)^2                 (bfloat16)
+//   GROUP_SCALE  the same row grouping;  out[m, n] = acc * row_scale[m]   (float32)
 //
 // A persistent grid of one block per SM walks the output tiles of 128 token rows x 256 weight
 // rows (SWIGLU: 128 gate + 128 up rows of the same 128 outputs), token tiles fastest, so that
@@ -30,7 +34,7 @@ namespace ifx {
 constexpr int kBM = 128, kBN = 256, kBK = 64, kGemmStages = 4;
 constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2, kStageBytes = kABytes + kBBytes;
 
-enum { GEMM_STORE = 0, GEMM_SWIGLU = 1 };
+enum { GEMM_STORE = 0, GEMM_SWIGLU = 1, GEMM_GROUP_RELU2 = 2, GEMM_GROUP_SCALE = 3 };
 
 __device__ __forceinline__ uint64_t gemm_smem_desc(uint32_t addr) {
   // K-major tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -67,8 +71,10 @@ template <int MODE>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     __nv_bfloat16* __restrict__ out, int M, int N, int K, int up_row_offset, int m_tiles, int n_tiles,
-                    int* __restrict__ error_flag) {
+                    int* __restrict__ error_flag, const int* __restrict__ tile_group, int group_rows,
+                    const float* __restrict__ row_scale) {
   constexpr int OUT_COLS = MODE == GEMM_SWIGLU ? kBN / 2 : kBN;     // output columns a tile makes
+  constexpr bool GROUPED = MODE == GEMM_GROUP_RELU2 || MODE == GEMM_GROUP_SCALE;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kGemmStages * kStageBytes);
@@ -107,7 +113,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int idx = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * kBM, n0 = (t / m_tiles) * OUT_COLS;
+        const int m0 = (t % m_tiles) * kBM;
+        int n0 = (t / m_tiles) * OUT_COLS;
+        if (GROUPED) {                                   // this tile's matrix of the stack, or nothing to do
+          const int grp = tile_group[t % m_tiles];
+          if (grp < 0) continue;
+          n0 += grp * group_rows;
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++idx) {
           const int s = idx % kGemmStages;
           if (idx >= kGemmStages) ok = mbar_wait(empty0 + 8 * s, ((idx / kGemmStages) & 1) ^ 1);
@@ -135,8 +147,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       int idx = 0, tile = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (GROUPED && tile_group[t % m_tiles] < 0) continue;       // skipped by every role alike: `tile` counts the others
         const int buf = tile & 1, use = tile >> 1;
+        ++tile;
         if (use > 0) ok = mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -162,8 +176,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quarter = warp & 3;                                     // TMEM lanes (token rows) of this warp
     int tile = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      if (GROUPED && tile_group[t % m_tiles] < 0) continue;
       const int buf = tile & 1, use = tile >> 1;
+      ++tile;
       const int m = (t % m_tiles) * kBM + quarter * 32 + lane, n0 = (t / m_tiles) * OUT_COLS;
       ok = mbar_wait(acc_full0 + 8 * buf, use & 1);
       if (!ok) {
@@ -173,6 +189,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
       __nv_bfloat16* row = out + (size_t)m * N + n0;
+      float* row_f = reinterpret_cast<float*>(out) + (size_t)m * N + n0;          // GROUP_SCALE writes float32
+      const float factor = (MODE == GEMM_GROUP_SCALE && m < M) ? row_scale[m] : 1.0f;
       const bool vec = (N % 8) == 0;                                  // rows start on 16-byte boundaries
 #pragma unroll 2
       for (int c = 0; c < OUT_COLS; c += 16) {
@@ -185,8 +203,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int j = 0; j < 16; ++j) {
           v[j] = __uint_as_float(g[j]);
           if (MODE == GEMM_SWIGLU) v[j] = __fdividef(v[j], 1.0f + __expf(-v[j])) * __uint_as_float(u[j]);
+          if (MODE == GEMM_GROUP_RELU2) v[j] = fmaxf(v[j], 0.0f) * fmaxf(v[j], 0.0f);
+          if (MODE == GEMM_GROUP_SCALE) v[j] *= factor;
         }
-        if (m < M) {
+        if (MODE == GEMM_GROUP_SCALE) {
+          if (m < M) {
+            if (vec && n0 + c + 16 <= N) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(row_f + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + c + j < N) row_f[c + j] = v[j];
+            }
+          }
+        } else if (m < M) {
           if (vec && n0 + c + 16 <= N) {
             uint4 lo = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
             uint4 hi = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]), pack_bf16(v[14], v[15]));
@@ -224,7 +255,8 @@ static int gemm_sm_count() {
 
 template <int MODE>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, int up_row_offset,
-                       int* error_flag, cudaStream_t stream) {
+                       int* error_flag, cudaStream_t stream, const int* tile_group = nullptr, int group_rows = 0,
+                       const float* row_scale = nullptr) {
   constexpr int OUT_COLS = MODE == GEMM_SWIGLU ? kBN / 2 : kBN;
   const size_t smem = 1024 + (size_t)kGemmStages * kStageBytes + (2 * kGemmStages + 4) * 8 + 16;
   static bool configured = false;
@@ -237,7 +269,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, void* out, 
   const int tiles = m_tiles * n_tiles;
   const int grid = tiles < gemm_sm_count() ? tiles : gemm_sm_count();
   gemm_tcgen05_kernel<MODE><<<grid, 192, smem, stream>>>(ma, mw, reinterpret_cast<__nv_bfloat16*>(out), M, N, K,
-                                                         up_row_offset, m_tiles, n_tiles, error_flag);
+                                                         up_row_offset, m_tiles, n_tiles, error_flag, tile_group,
+                                                         group_rows, row_scale);
   IFX_CHECK_LAUNCH();
   return 0;
 }
@@ -262,5 +295,29 @@ extern "C" int ifx_gemm_tcgen05(const void* act, const void* W, void* out, int M
   if (rc) return rc;
   if (mode == GEMM_STORE) return launch_gemm<GEMM_STORE>(ma, mw, out, M, N, K, 0, error_flag, stream);
   if (mode == GEMM_SWIGLU) return launch_gemm<GEMM_SWIGLU>(ma, mw, out, M, N, K, up_row_offset, error_flag, stream);
+  return IFX_E_BADARG;
+}
+
+// Rows sorted into groups of whole 128-row tiles against a stack of matrices (see GROUP_RELU2 / GROUP_SCALE above).
+// act [M, K] bfloat16 with M a multiple of 128; W [groups * group_rows, K]; tile_group: int32 [M / 128] on the device,
+// the matrix of every row tile or a negative number for a tile that is not used.
+// mode 2: out [M, N] bfloat16 = relu(act . W_g[:N]^T)^2.   mode 3: out [M, N] float32 = (act . W_g[:N]^T) * row_scale[m].
+extern "C" int ifx_gemm_tcgen05_grouped(const void* act, const void* W, void* out, int M, int N, int K, int groups,
+                                        int group_rows, const int* tile_group, const float* row_scale, int mode,
+                                        int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || M % kBM || groups <= 0 || N > group_rows || error_flag == nullptr || out == nullptr ||
+      tile_group == nullptr)
+    return IFX_E_BADARG;
+  if (mode == GEMM_GROUP_SCALE && row_scale == nullptr) return IFX_E_BADARG;
+  CUtensorMap ma, mw;
+  int rc = weight_tensor_map(&mw, W, (long long)groups * group_rows, K, 128);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16(&ma, act, M, K, kBM);
+  if (rc) return rc;
+  if (mode == GEMM_GROUP_RELU2)
+    return launch_gemm<GEMM_GROUP_RELU2>(ma, mw, out, M, N, K, 0, error_flag, stream, tile_group, group_rows, row_scale);
+  if (mode == GEMM_GROUP_SCALE)
+    return launch_gemm<GEMM_GROUP_SCALE>(ma, mw, out, M, N, K, 0, error_flag, stream, tile_group, group_rows, row_scale);
   return IFX_E_BADARG;
 }

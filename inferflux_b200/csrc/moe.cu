@@ -7,7 +7,16 @@
 //   moe_down      out[t] = sum over the token's choices, in their order, of weight * (W_down[e] act[p]), or
 //                 weight * h[t] for an expert without weights
 //
-// These are the kernels of the float32 run and of steps with few tokens: a warp makes one output number as a dot
+// Steps with many tokens in bfloat16 sort their (token, choice) pairs by expert instead and multiply whole tiles on the
+// tensor cores (the grouped modes of gemm_tcgen05.cu):
+//
+//   moe_sort      every expert's pairs get a stretch of rows that starts on a multiple of 128; per row the pair it
+//                 holds (or -1) and the pair's weight (or 0); per 128-row tile its expert (or -1); per pair its row
+//   moe_gather    rows[r] = h[token of the pair in row r], zeros for a row without a pair
+//   moe_combine   out[t] = sum over the token's choices, in their order, of y[row of the pair] (already weighted), or
+//                 weight * h[t] for an expert without weights
+//
+// The kernels below the sort are those of the float32 run and of steps with few tokens: a warp makes one output number as a dot
 // product (lanes stride the inner size, then a shuffle tree), so every sum has an order that depends on the sizes
 // alone.  Expert weights are stacked: up [experts, ff, width], down [experts, width, ff].
 #include "common.cuh"
@@ -70,12 +79,40 @@ __device__ __forceinline__ float dot_lanes(const T* __restrict__ w, const float*
   return warp_sum(s);
 }
 
+// bfloat16 weights in 16-byte pieces, four of them in flight per lane, when the row allows it.
+template <>
+__device__ __forceinline__ float dot_lanes<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ a,
+                                                          int n, int lane) {
+  float s = 0.0f;
+  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    const uint4* w8 = reinterpret_cast<const uint4*>(w);
+    const int chunks = n >> 3;
+    auto use = [&](uint4 raw, int chunk) {
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float4 a0 = *reinterpret_cast<const float4*>(a + 8 * chunk), a1 = *reinterpret_cast<const float4*>(a + 8 * chunk + 4);
+      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+      const float2 f2 = __bfloat1622float2(p2[2]), f3 = __bfloat1622float2(p2[3]);
+      s = fmaf(f0.x, a0.x, s); s = fmaf(f0.y, a0.y, s); s = fmaf(f1.x, a0.z, s); s = fmaf(f1.y, a0.w, s);
+      s = fmaf(f2.x, a1.x, s); s = fmaf(f2.y, a1.y, s); s = fmaf(f3.x, a1.z, s); s = fmaf(f3.y, a1.w, s);
+    };
+    int i = lane;
+    for (; i + 96 < chunks; i += 128) {
+      const uint4 r0 = __ldg(w8 + i), r1 = __ldg(w8 + i + 32), r2 = __ldg(w8 + i + 64), r3 = __ldg(w8 + i + 96);
+      use(r0, i); use(r1, i + 32); use(r2, i + 64); use(r3, i + 96);
+    }
+    for (; i < chunks; i += 32) use(__ldg(w8 + i), i);
+  } else {
+    for (int i = lane; i < n; i += 32) s = fmaf(__bfloat162float(w[i]), a[i], s);
+  }
+  return warp_sum(s);
+}
+
 constexpr int kMoeWarps = 8;
 
 template <typename T>
 __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
                               T* __restrict__ act, int top, int experts, int width, int ff, int rows_per_block) {
-  extern __shared__ float h_s[];
+  extern __shared__ __align__(16) float h_s[];
   const int p = blockIdx.x;
   const int e = ids[p];
   if (e >= experts || e < 0) return;
@@ -95,7 +132,7 @@ template <typename T, typename TO>
 __global__ void moe_down_kernel(const T* __restrict__ h, const T* __restrict__ act, const T* __restrict__ w_down,
                                 const int* __restrict__ ids, const float* __restrict__ weights, TO* __restrict__ out,
                                 int top, int experts, int width, int ff, int rows_per_block) {
-  extern __shared__ float a_s[];
+  extern __shared__ __align__(16) float a_s[];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c0 = blockIdx.y * rows_per_block, c1 = min(width, c0 + rows_per_block);
@@ -138,6 +175,73 @@ __global__ void moe_down_kernel(const T* __restrict__ h, const T* __restrict__ a
   }
 }
 
+// One block.  counts/offset/cursor live in shared memory: experts <= kMaxRouterOutputs.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ weights,
+                                                        int pairs, int experts, int* __restrict__ row_pair,
+                                                        float* __restrict__ row_scale, int* __restrict__ tile_group,
+                                                        int* __restrict__ pair_row, int rows_cap) {
+  __shared__ int count_s[kMaxRouterOutputs], offset_s[kMaxRouterOutputs], cursor_s[kMaxRouterOutputs];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count_s[e] = cursor_s[e] = 0;
+  for (int r = threadIdx.x; r < rows_cap; r += blockDim.x) {
+    row_pair[r] = -1;
+    row_scale[r] = 0.0f;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) atomicAdd(&count_s[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int row = 0;
+    for (int e = 0; e < experts; ++e) {
+      offset_s[e] = row;
+      const int tiles = (count_s[e] + 127) / 128;
+      for (int i = 0; i < tiles; ++i) tile_group[row / 128 + i] = e;
+      row += tiles * 128;
+    }
+    for (int tile = row / 128; tile < rows_cap / 128; ++tile) tile_group[tile] = -1;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    int row = -1;
+    if (e >= 0 && e < experts) {
+      row = offset_s[e] + atomicAdd(&cursor_s[e], 1);      // which row inside the stretch does not change a row's result
+      row_pair[row] = p;
+      row_scale[row] = weights[p];
+    }
+    pair_row[p] = row;
+  }
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ h, const int* __restrict__ row_pair,
+                                  __nv_bfloat16* __restrict__ rows, int top, int width8) {
+  const int r = blockIdx.x;
+  const int p = row_pair[r];
+  const uint4* src = p >= 0 ? reinterpret_cast<const uint4*>(h) + (size_t)(p / top) * width8 : nullptr;
+  uint4* dst = reinterpret_cast<uint4*>(rows) + (size_t)r * width8;
+  for (int i = threadIdx.x; i < width8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+}
+
+template <typename TO>
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ y,
+                                   const int* __restrict__ ids, const float* __restrict__ weights,
+                                   const int* __restrict__ pair_row, TO* __restrict__ out, int top, int experts,
+                                   int width) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < top; ++k) {
+      const int p = t * top + k;
+      const int row = pair_row[p];
+      if (row >= 0) acc += y[(size_t)row * width + c];
+      else acc = fmaf(weights[p], to_f32(h[(size_t)t * width + c]), acc);
+    }
+    out[(size_t)t * width + c] = from_f32<TO>(acc);
+  }
+}
+
 }  // namespace ifx
 
 using namespace ifx;
@@ -161,7 +265,7 @@ int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const i
   if (T <= 0) return 0;
   if (top <= 0 || experts < 0 || width <= 0 || ff <= 0) return IFX_E_BADARG;
   if ((size_t)width * 4 > 160 * 1024 || (size_t)ff * 4 > 160 * 1024) return IFX_E_TOOBIG;
-  const int up_rows = 32, down_rows = 64;               // 64 = 8 warps x 8 rows
+  const int up_rows = 32, down_rows = T <= 64 ? 16 : 64;  // few tokens: more blocks, so that more bytes are in flight
   dim3 grid_up(T * top, (ff + up_rows - 1) / up_rows), grid_down(T, (width + down_rows - 1) / down_rows);
   const size_t smem_up = (size_t)width * 4, smem_down = (size_t)ff * 4;
 #define IFX_MOE(TT, TO)                                                                                           \
@@ -183,6 +287,43 @@ int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const i
   else if (dtype == IFX_DT_BF16 && out_dtype == IFX_DT_F32) IFX_MOE(__nv_bfloat16, float);
   else return IFX_E_DTYPE;
 #undef IFX_MOE
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+// Rows that the sorted form needs at most: every expert's stretch is rounded up to whole tiles of 128.
+int ifx_moe_sorted_rows(int pairs, int experts) {
+  return (pairs + experts * 127 + 127) / 128 * 128;
+}
+
+int ifx_moe_sort(const int* ids, const float* weights, int pairs, int experts, int* row_pair, float* row_scale,
+                 int* tile_group, int* pair_row, int rows_cap, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (experts <= 0 || experts > kMaxRouterOutputs || rows_cap % 128 || rows_cap < ifx_moe_sorted_rows(pairs, experts))
+    return IFX_E_BADARG;
+  moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, weights, pairs, experts, row_pair, row_scale, tile_group, pair_row, rows_cap);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+int ifx_moe_gather(const void* h, const int* row_pair, void* rows, int rows_cap, int top, int width, cudaStream_t stream) {
+  if (rows_cap <= 0) return 0;
+  if (width % 8 || (uintptr_t)h % 16 || (uintptr_t)rows % 16) return IFX_E_ALIGN;
+  moe_gather_kernel<<<rows_cap, 128, 0, stream>>>((const __nv_bfloat16*)h, row_pair, (__nv_bfloat16*)rows, top, width / 8);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+int ifx_moe_combine(const void* h, const float* y, const int* ids, const float* weights, const int* pair_row, void* out,
+                    int T, int top, int experts, int width, int out_dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (out_dtype == IFX_DT_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)h, y, ids, weights, pair_row,
+                                                             (__nv_bfloat16*)out, top, experts, width);
+  else if (out_dtype == IFX_DT_F32)
+    moe_combine_kernel<float><<<T, 256, 0, stream>>>((const __nv_bfloat16*)h, y, ids, weights, pair_row, (float*)out, top,
+                                                     experts, width);
+  else return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();
   return 0;
 }

@@ -146,7 +146,8 @@ class CudaKernels:
                    "ifx_latent_attention_mma_supports", "ifx_gemm_cublas_bf16_batched", "ifx_gemm_skinny_act",
                    "ifx_attention_generic_ex", "ifx_norm_rope_append", "ifx_token_shift_mix", "ifx_cast_rows",
                    "ifx_wkv_scan", "ifx_moe_route", "ifx_moe_experts", "ifx_tanh_rows",
-                   "ifx_attention_prefill_bf16_ex", "ifx_attention_decode_bf16_ex"):
+                   "ifx_attention_prefill_bf16_ex", "ifx_attention_decode_bf16_ex", "ifx_moe_sorted_rows", "ifx_moe_sort",
+                   "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
@@ -1080,12 +1081,48 @@ class CudaKernels:
         _need(h.is_contiguous() and (not experts or (w_up.dtype == h.dtype and w_down.dtype == h.dtype and w_up.is_contiguous()
               and w_down.is_contiguous() and tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff))),
               "moe_experts: stacked expert weights in the activations' dtype")
+        if (experts and h.dtype == torch.bfloat16 and T * top >= self.MOE_TILES_MIN_PAIRS and width % 8 == 0 and ff % 8 == 0
+                and h.data_ptr() % 16 == 0 and os.environ.get("INFERFLUX_B200_MOE_TILES", "1") != "0"):
+            return self._moe_experts_tiles(h, w_up, w_down, ids, weights, experts, out_dtype)
         act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
         out = torch.empty((T, width), dtype=out_dtype, device=h.device)
         _check(self.lib.ifx_moe_experts(_ptr(h), _ptr(w_up if experts else None), _ptr(w_down if experts else None), _ptr(ids),
                                         _ptr(weights), _ptr(act), _ptr(out), T, top, int(experts), width, ff, _DT[h.dtype],
                                         _DT[out_dtype], _stream()), "moe_experts")
         self.launches += 2 if experts else 1
+        return out
+
+    # From this many (token, choice) pairs on, the experts run as sorted 128-row tiles on the tensor cores.
+    MOE_TILES_MIN_PAIRS = 512
+
+    def _moe_experts_tiles(self, h, w_up, w_down, ids, weights, experts, out_dtype):
+        """bfloat16, many tokens: pairs sorted by expert into stretches of whole 128-row tiles, two grouped tcgen05
+        products (relu^2 in the first one's epilogue, the pair's weight in the second's), then the sum per token."""
+        T, width = h.shape
+        top, ff = ids.shape[1], w_up.shape[1]
+        pairs = T * top
+        cap = int(self.lib.ifx_moe_sorted_rows(pairs, int(experts)))
+        dev = h.device
+        row_pair = torch.empty(cap, dtype=torch.int32, device=dev)
+        row_scale = torch.empty(cap, dtype=torch.float32, device=dev)
+        tile_group = torch.empty(cap // 128, dtype=torch.int32, device=dev)
+        pair_row = torch.empty(pairs, dtype=torch.int32, device=dev)
+        _check(self.lib.ifx_moe_sort(_ptr(ids), _ptr(weights), pairs, int(experts), _ptr(row_pair), _ptr(row_scale),
+                                     _ptr(tile_group), _ptr(pair_row), cap, _stream()), "moe_sort")
+        rows = torch.empty((cap, width), dtype=torch.bfloat16, device=dev)
+        _check(self.lib.ifx_moe_gather(_ptr(h), _ptr(row_pair), _ptr(rows), cap, top, width, _stream()), "moe_gather")
+        act = torch.empty((cap, ff), dtype=torch.bfloat16, device=dev)
+        _check(self.lib.ifx_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts), ff,
+                                                 _ptr(tile_group), _ptr(None), 2, _ptr(self.error_flag), _stream()),
+               "moe experts (up, tiles)")
+        y = torch.empty((cap, width), dtype=torch.float32, device=dev)
+        _check(self.lib.ifx_gemm_tcgen05_grouped(_ptr(act), _ptr(w_down), _ptr(y), cap, width, ff, int(experts), width,
+                                                 _ptr(tile_group), _ptr(row_scale), 3, _ptr(self.error_flag), _stream()),
+               "moe experts (down, tiles)")
+        out = torch.empty((T, width), dtype=out_dtype, device=dev)
+        _check(self.lib.ifx_moe_combine(_ptr(h), _ptr(y), _ptr(ids), _ptr(weights), _ptr(pair_row), _ptr(out), T, top,
+                                        int(experts), width, _DT[out_dtype], _stream()), "moe_combine")
+        self.launches += 5
         return out
 
     # ---------------------------------------------------------------- sampling

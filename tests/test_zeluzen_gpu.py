@@ -163,6 +163,34 @@ def test_experts_against_the_plain_statement(cuda_kernels, dtype, tol, sizes):
         assert float((got2.cpu() - 0.5 * h.float()).abs().max()) < 1e-6
 
 
+@pytest.mark.parametrize("sizes", [(64, 24, 3, 2, 2, 300), (256, 96, 6, 1, 4, 700), (136, 200, 16, 0, 8, 130), (72, 40, 9, 3, 1, 1100)])
+def test_experts_as_sorted_tiles_against_the_per_token_kernels(cuda_kernels, sizes, monkeypatch):
+    """Many tokens in bfloat16: the sorted tensor-core tiles against the per-token kernels and the plain statement,
+    with experts that nobody chose, experts with more than one tile of rows, and input-passing experts."""
+    width, ff, experts, identity, top, T = sizes
+    bf = torch.bfloat16
+    h = _rnd(T, width, seed=1).to(bf)
+    up = _rnd(experts, ff, width, seed=2, scale=width ** -0.5).to(bf)
+    down = _rnd(experts, width, ff, seed=3, scale=ff ** -0.5).to(bf)
+    g = torch.Generator().manual_seed(4)
+    pool = torch.tensor([e for e in range(experts + identity) if e != 1])            # expert 1 is never chosen
+    ids = torch.stack([pool[torch.randperm(len(pool), generator=g)[:top]] for _ in range(T)]).to(torch.int32)
+    ids[: T // 2, 0] = 0                                                              # expert 0 gets rows for several tiles
+    wts = torch.rand(T, top, generator=g)
+    args = (h.to(DEV), up.to(DEV), down.to(DEV), ids.to(DEV), wts.to(DEV), experts, bf)
+    assert T * top >= cuda_kernels.MOE_TILES_MIN_PAIRS
+    launches = cuda_kernels.launches
+    tiles = cuda_kernels.moe_experts(*args).float().cpu()
+    assert cuda_kernels.launches - launches == 5
+    cuda_kernels.check_errors()
+    monkeypatch.setenv("INFERFLUX_B200_MOE_TILES", "0")
+    rows = cuda_kernels.moe_experts(*args).float().cpu()
+    want = PlainKernels(wide=True).moe_experts(h, up, down, ids, wts, experts, F64)
+    scale = max(1.0, float(want.abs().max()))
+    assert float((tiles.double() - want).abs().max()) <= 2e-2 * scale and float((rows.double() - want).abs().max()) <= 2e-2 * scale
+    assert float((tiles - rows).abs().max()) <= 2e-2 * scale
+
+
 # ------------------------------------------------------------------ attention: head norms, chunks, sink, value size
 
 def _attention_setup(cuda_kernels, dtype, nq, nkv, d, dv, page, n, seed):
