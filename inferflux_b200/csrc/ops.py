@@ -1054,7 +1054,7 @@ class CudaKernels:
         _check(self.lib.ifx_wkv_scan(
             _ptr(r), _ptr(k), _ptr(v), _ptr(w_raw), _ptr(g), _ptr(w0), _ptr(u), _ptr(norm_w), ctypes.c_float(eps),
             _ptr(state), ctypes.c_void_p(state.data_ptr() + 4 * prev_offset), ctypes.c_longlong(state.shape[1]), _ptr(x), C,
-            _ptr(ctx.cu_seqlens), _ptr(ctx.req_slot), _ptr(scratch), _ptr(y), ctx.num_requests, heads, dim, _DT[out_dtype],
+            _ptr(ctx.cu_seqlens), _ptr(ctx.req_slot), _ptr(scratch), _ptr(y), ctx.num_requests, T, heads, dim, _DT[out_dtype],
             _stream()), "wkv_scan")
         self.launches += 1
         return y

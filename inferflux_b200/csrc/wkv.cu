@@ -15,10 +15,10 @@
 // The scan is sequential in the tokens of a request, so what a position gets does not depend on how the
 // tokens were cut into steps: every sum has one order, fixed by the head size alone.
 //
-// Layout of a thread block of the scan: thread (j, s) owns value channel j and the key channels
-// i = s, s + KS, s + 2 KS, ... of S in registers (KS a power of two up to 32; the KS threads of a channel are
-// neighbours in a warp and add their shares by shuffles).  r, k, w and v of up to 16 tokens are staged in
-// shared memory at a time, so the block synchronises three times per 16 tokens, not per token.
+// Layout of a thread block of the scan: thread (j, s) owns value channel j and four (for the largest heads eight)
+// key channels i = s, s + KS, s + 2 KS, ... of S in registers (KS a power of two up to 32 that depends on the
+// head size alone; the KS threads of a channel are neighbours in a warp and add their shares by shuffles).  r, k, w and v of up to 32 tokens arrive in shared
+// memory at a time, so the block synchronises three times per 32 tokens, not per token.
 #include "common.cuh"
 
 namespace ifx {
@@ -54,99 +54,170 @@ __global__ void tanh_rows_kernel(T* __restrict__ z, long long n) {
     z[i] = from_f32<T>(tanhf(to_f32(z[i])));
 }
 
-constexpr int kScanTokens = 16;      // tokens staged at a time
+constexpr int kScanThreads = 1024;   // the most threads a block of the scan has
 
-template <int RMAX, typename TO>
-__global__ void __launch_bounds__(1024) wkv_scan_kernel(
+__device__ __forceinline__ void cp_async_4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// out / rms(out) * norm_w * silu(g) for one (token, head), by one warp: the same code whether the scan's block or
+// the kernel of its own runs it, so that both give the same bits.
+template <typename TO>
+__device__ __forceinline__ void wkv_head_norm(const float* __restrict__ o, const float* __restrict__ g,
+                                              const float* __restrict__ norm_w, float eps, TO* __restrict__ y, int D,
+                                              int lane) {
+  float ss = 0.0f;
+  for (int i = lane; i < D; i += 32) ss = fmaf(o[i], o[i], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int i = lane; i < D; i += 32) {
+    const float gate = g[i];
+    y[i] = from_f32<TO>(o[i] * inv * norm_w[i] * (gate / (1.0f + expf(-gate))));
+  }
+}
+
+// grid (requests, heads, column groups): a block owns `DC` value channels of one head of one request.  A column of S
+// depends on no other column, so the split changes no sum.  Inputs of `TB` tokens at a time arrive by cp.async in
+// one of two buffers while the tokens of the other are worked on.  With one column group the block norms its own
+// outputs at the end (`fused_norm`); otherwise wkv_norm_kernel does.
+template <int KS, int R, typename TO>
+__global__ void __launch_bounds__(kScanThreads) wkv_scan_kernel(
     const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ w_raw, const float* __restrict__ g, const float* __restrict__ w0,
     const float* __restrict__ u, const float* __restrict__ norm_w, float eps, float* __restrict__ s_state,
     float* __restrict__ prev_state, long long slot_stride, const float* __restrict__ x, int C,
     const int* __restrict__ cu_seqlens, const int* __restrict__ req_slot, float* __restrict__ o_scratch,
-    TO* __restrict__ y, int H, int D, int KS) {
-  extern __shared__ float smem[];
-  float* r_s = smem;                                 // [kScanTokens][D]
-  float* k_s = r_s + kScanTokens * D;
-  float* w_s = k_s + kScanTokens * D;
-  float* v_s = w_s + kScanTokens * D;
-  float* b_s = v_s + kScanTokens * D;                // [kScanTokens] bonus sums
-  const int req = blockIdx.x, head = blockIdx.y;
+    TO* __restrict__ y, int H, int D, int DC, int TB, int fused_norm, int wide_copies) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int DP = KS * R;                         // a staged row of r, k or w: D numbers, then zeros up to KS * R
+  const int per_buf = TB * (3 * DP + DC);
+  float* b_s = smem + 2 * per_buf;                   // [TB] bonus sums of the chunk at work
+  const int req = blockIdx.x, head = blockIdx.y, j0 = blockIdx.z * DC;
+  const int cols = min(DC, D - j0);                  // value channels of this block
   const int lo = cu_seqlens[req], hi = cu_seqlens[req + 1];
   const int slot = req_slot[req];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const int j = tid / KS, s = tid % KS;
-  const bool active = j < D;
+  const int jl = tid / KS, s = tid % KS;
+  const bool active = jl < cols;
+  const int j = j0 + jl;
   const int HD = H * D;
   float* S_g = s_state + (long long)slot * slot_stride + (size_t)head * D * D;
-  float S[RMAX];
+  float S[R];
 #pragma unroll
-  for (int m = 0; m < RMAX; ++m) {
+  for (int m = 0; m < R; ++m) {
     const int i = s + KS * m;
     S[m] = (active && i < D) ? S_g[(size_t)i * D + j] : 0.0f;
   }
-  for (int t0 = lo; t0 < hi; t0 += kScanTokens) {
-    const int nt = min(kScanTokens, hi - t0);
-    for (int idx = tid; idx < nt * D; idx += blockDim.x) {
-      const int tt = idx / D, i = idx % D;
-      const size_t src = (size_t)(t0 + tt) * HD + (size_t)head * D + i;
-      r_s[idx] = r[src];
-      k_s[idx] = k[src];
-      v_s[idx] = v[src];
-      w_s[idx] = expf(-expf(w_raw[src] + w0[head * D + i]));
+  // what lies behind a row's D numbers stays zero for good: a key channel that does not exist adds nothing
+  for (int idx = tid; idx < 2 * per_buf + TB; idx += blockDim.x) smem[idx] = 0.0f;
+  __syncthreads();
+  auto fetch = [&](int t0, int buf) {                // tokens [t0, t0 + TB) of the span into buffer `buf`
+    const int nt = min(TB, hi - t0);
+    float* r_s = smem + buf * per_buf;
+    float* k_s = r_s + TB * DP;
+    float* w_s = k_s + TB * DP;
+    float* v_s = w_s + TB * DP;
+    if (wide_copies) {
+      const int d4 = D >> 2, c4 = cols >> 2;
+      for (int idx = tid; idx < nt * d4; idx += blockDim.x) {
+        const int tt = idx / d4, i = (idx % d4) * 4;
+        const size_t src = (size_t)(t0 + tt) * HD + (size_t)head * D + i;
+        cp_async_16(r_s + tt * DP + i, r + src);
+        cp_async_16(k_s + tt * DP + i, k + src);
+        cp_async_16(w_s + tt * DP + i, w_raw + src);
+      }
+      for (int idx = tid; idx < nt * c4; idx += blockDim.x) {
+        const int tt = idx / c4, i = (idx % c4) * 4;
+        cp_async_16(v_s + tt * DC + i, v + (size_t)(t0 + tt) * HD + (size_t)head * D + j0 + i);
+      }
+    } else {
+      for (int idx = tid; idx < nt * D; idx += blockDim.x) {
+        const int tt = idx / D, i = idx % D;
+        const size_t src = (size_t)(t0 + tt) * HD + (size_t)head * D + i;
+        cp_async_4(r_s + tt * DP + i, r + src);
+        cp_async_4(k_s + tt * DP + i, k + src);
+        cp_async_4(w_s + tt * DP + i, w_raw + src);
+      }
+      for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
+        const int tt = idx / cols, i = idx % cols;
+        cp_async_4(v_s + tt * DC + i, v + (size_t)(t0 + tt) * HD + (size_t)head * D + j0 + i);
+      }
     }
+  };
+  if (lo < hi) fetch(lo, 0);
+  cp_async_commit();
+  int buf = 0;
+  for (int t0 = lo; t0 < hi; t0 += TB, buf ^= 1) {
+    const int nt = min(TB, hi - t0);
+    if (t0 + TB < hi) fetch(t0 + TB, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();                              // everything but the copies just asked for has landed
     __syncthreads();
-    for (int tt = warp; tt < nt; tt += nwarps) {       // the bonus of the present token: one number per token
+    float* r_s = smem + buf * per_buf;
+    float* k_s = r_s + TB * DP;
+    float* w_s = k_s + TB * DP;
+    float* v_s = w_s + TB * DP;
+    for (int idx = tid; idx < nt * D; idx += blockDim.x) {        // the decay, where the exponent was copied to
+      const int tt = idx / D, i = idx % D;
+      w_s[tt * DP + i] = expf(-expf(w_s[tt * DP + i] + w0[head * D + i]));
+    }
+    for (int tt = warp; tt < nt; tt += nwarps) {                   // the bonus of the present token: one number per token
       float b = 0.0f;
-      for (int i = lane; i < D; i += 32) b = fmaf(r_s[tt * D + i] * u[head * D + i], k_s[tt * D + i], b);
+      for (int i = lane; i < D; i += 32) b = fmaf(r_s[tt * DP + i] * u[head * D + i], k_s[tt * DP + i], b);
       b = warp_sum(b);
       if (lane == 0) b_s[tt] = b;
     }
     __syncthreads();
+#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
-      const float* rr = r_s + tt * D;
-      const float* kk = k_s + tt * D;
-      const float* ww = w_s + tt * D;
-      const float vj = active ? v_s[tt * D + j] : 0.0f;
+      const float* rr = r_s + tt * DP + s;
+      const float* kk = k_s + tt * DP + s;
+      const float* ww = w_s + tt * DP + s;
+      const float vj = active ? v_s[tt * DC + jl] : 0.0f;
       float acc = 0.0f;
 #pragma unroll
-      for (int m = 0; m < RMAX; ++m) {
-        const int i = s + KS * m;
-        if (i < D) {
-          acc = fmaf(rr[i], S[m], acc);
-          S[m] = fmaf(ww[i], S[m], kk[i] * vj);
-        }
+      for (int m = 0; m < R; ++m) {
+        acc = fmaf(rr[KS * m], S[m], acc);
+        S[m] = fmaf(ww[KS * m], S[m], kk[KS * m] * vj);
       }
+#pragma unroll
       for (int o = 1; o < KS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (active && s == 0) o_scratch[(size_t)(t0 + tt) * HD + (size_t)head * D + j] = fmaf(b_s[tt], vj, acc);
     }
-    __syncthreads();
+    __syncthreads();                                 // the buffer is free for the copies of the chunk after next
   }
+  cp_async_wait<0>();
 #pragma unroll
-  for (int m = 0; m < RMAX; ++m) {
+  for (int m = 0; m < R; ++m) {
     const int i = s + KS * m;
     if (active && i < D) S_g[(size_t)i * D + j] = S[m];
   }
-  if (head == 0 && hi > lo) {                          // the step's last input is the next step's "token before"
+  if (head == 0 && blockIdx.z == 0 && hi > lo) {       // the step's last input is the next step's "token before"
     float* p = prev_state + (long long)slot * slot_stride;
     const float* last = x + (size_t)(hi - 1) * C;
     for (int i = tid; i < C; i += blockDim.x) p[i] = last[i];
   }
+  if (!fused_norm) return;
   // the block's own writes to o_scratch are visible to it after the barrier at the end of the loop
   for (int t = lo + warp; t < hi; t += nwarps) {
     const size_t base = (size_t)t * HD + (size_t)head * D;
-    float ss = 0.0f;
-    for (int i = lane; i < D; i += 32) {
-      const float o = o_scratch[base + i];
-      ss = fmaf(o, o, ss);
-    }
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-    for (int i = lane; i < D; i += 32) {
-      const float gate = g[base + i];
-      const float sg = gate / (1.0f + expf(-gate));
-      y[base + i] = from_f32<TO>(o_scratch[base + i] * inv * norm_w[head * D + i] * sg);
-    }
+    wkv_head_norm<TO>(o_scratch + base, g + base, norm_w + head * D, eps, y + base, D, lane);
   }
+}
+
+template <typename TO>
+__global__ void wkv_norm_kernel(const float* __restrict__ o, const float* __restrict__ g, const float* __restrict__ norm_w,
+                                float eps, TO* __restrict__ y, long long items, int H, int D) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int head = (int)(item % H);
+  const size_t base = (size_t)item * D;              // item = token * H + head
+  wkv_head_norm<TO>(o + base, g + base, norm_w + head * D, eps, y + base, D, threadIdx.x & 31);
 }
 
 }  // namespace ifx
@@ -201,34 +272,54 @@ int ifx_tanh_rows(void* z, long long n, int dtype, cudaStream_t stream) {
 int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_raw, const float* g, const float* w0,
                  const float* u, const float* norm_w, float eps, float* s_state, float* prev_state,
                  long long slot_stride, const float* x, int C, const int* cu_seqlens, const int* req_slot,
-                 float* o_scratch, void* y, int num_requests, int H, int D, int out_dtype, cudaStream_t stream) {
-  if (num_requests <= 0) return 0;
+                 float* o_scratch, void* y, int num_requests, int num_tokens, int H, int D, int out_dtype,
+                 cudaStream_t stream) {
+  if (num_requests <= 0 || num_tokens <= 0) return 0;
   if (H <= 0 || D <= 0 || D > 256 || H > 65535) return IFX_E_BADARG;
-  int rmax = 16, ks = 1;
-  while (ks < 32 && (D + ks - 1) / ks > rmax) ks *= 2;
-  if ((D + ks - 1) / ks > rmax || D * ks > 1024) {       // large heads: more of S per thread
-    rmax = 64;
-    ks = 1;
-    while (ks < 32 && (D + ks - 1) / ks > rmax) ks *= 2;
-    if ((D + ks - 1) / ks > rmax || D * ks > 1024) return IFX_E_TOOBIG;
-  }
-  const int threads = (D * ks + 31) / 32 * 32;
-  const size_t smem = ((size_t)4 * kScanTokens * D + kScanTokens) * sizeof(float);
-  dim3 grid(num_requests, H);
-#define IFX_SCAN(R, TO)                                                                                          \
+  // threads per value channel (a power of two that depends on the head size alone, so that a sum's order does too)
+  // and key channels per thread: four, eight for the largest heads
+  int ks = 1;
+  while (ks < 32 && ks * 4 < D) ks *= 2;
+  const int rows = ks * 4 >= D ? 4 : 8;
+  const int dp = ks * rows;
+  // value channels per block: as many as a block holds; fewer while the grid does not fill the SMs
+  int dc = D;
+  while (dc * ks > kScanThreads) dc = (dc + 1) / 2;
+  while ((long long)num_requests * H * ((D + dc - 1) / dc) < 148 && dc * ks > 64 && dc % 8 == 0) dc /= 2;
+  const int groups = (D + dc - 1) / dc;
+  const int threads = (dc * ks + 31) / 32 * 32;
+  const int longest = num_tokens - (num_requests - 1);                 // no span is longer than this
+  int tb = longest < 32 ? (longest < 16 ? 16 : longest) : 32;
+  while (tb > 4 && ((size_t)2 * tb * (3 * dp + dc) + tb) * sizeof(float) > 160 * 1024) tb /= 2;
+  const size_t smem = ((size_t)2 * tb * (3 * dp + dc) + tb) * sizeof(float);
+  const int wide = (D % 4 == 0 && dc % 4 == 0 && ((uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)w_raw) % 16 == 0) ? 1 : 0;
+  const int fused = groups == 1 ? 1 : 0;
+  dim3 grid(num_requests, H, groups);
+#define IFX_SCAN(KS_, R_, TO)                                                                                    \
   do {                                                                                                           \
-    auto kern = wkv_scan_kernel<R, TO>;                                                                          \
+    auto kern = wkv_scan_kernel<KS_, R_, TO>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     kern<<<grid, threads, smem, stream>>>(r, k, v, w_raw, g, w0, u, norm_w, eps, s_state, prev_state, slot_stride, \
-                                          x, C, cu_seqlens, req_slot, o_scratch, (TO*)y, H, D, ks);              \
+                                          x, C, cu_seqlens, req_slot, o_scratch, (TO*)y, H, D, dc, tb, fused, wide); \
+    if (!fused) {                                                                                                \
+      const long long items = (long long)num_tokens * H;                                                        \
+      wkv_norm_kernel<TO><<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(o_scratch, g, norm_w, eps, (TO*)y, items, H, D); \
+    }                                                                                                            \
   } while (0)
-  if (out_dtype == IFX_DT_F32) {
-    if (rmax == 16) IFX_SCAN(16, float); else IFX_SCAN(64, float);
-  } else if (out_dtype == IFX_DT_BF16) {
-    if (rmax == 16) IFX_SCAN(16, __nv_bfloat16); else IFX_SCAN(64, __nv_bfloat16);
-  } else {
-    return IFX_E_DTYPE;
-  }
+#define IFX_SCAN_KS(TO)                                   \
+  do {                                                    \
+    if (rows == 8) IFX_SCAN(32, 8, TO);                   \
+    else if (ks == 1) IFX_SCAN(1, 4, TO);                 \
+    else if (ks == 2) IFX_SCAN(2, 4, TO);                 \
+    else if (ks == 4) IFX_SCAN(4, 4, TO);                 \
+    else if (ks == 8) IFX_SCAN(8, 4, TO);                 \
+    else if (ks == 16) IFX_SCAN(16, 4, TO);               \
+    else IFX_SCAN(32, 4, TO);                             \
+  } while (0)
+  if (out_dtype == IFX_DT_F32) IFX_SCAN_KS(float);
+  else if (out_dtype == IFX_DT_BF16) IFX_SCAN_KS(__nv_bfloat16);
+  else return IFX_E_DTYPE;
+#undef IFX_SCAN_KS
 #undef IFX_SCAN
   IFX_CHECK_LAUNCH();
   return 0;
