@@ -107,6 +107,65 @@ __device__ __forceinline__ float dot_lanes<__nv_bfloat16>(const __nv_bfloat16* _
   return warp_sum(s);
 }
 
+// NR rows of bfloat16 weights against the same staged vector, their 16-byte loads in flight together (a row alone
+// leaves a lane with too few bytes under way to keep the memory busy).  Each row's sum is added in the order dot_lanes uses.
+template <int NR>
+__device__ __forceinline__ void dot_lanes_rows(const __nv_bfloat16* const (&w)[NR], const float* __restrict__ a, int n,
+                                               int lane, float (&out)[NR]) {
+  float s[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) s[r] = 0.0f;
+  bool wide = (n & 7) == 0;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) wide = wide && (reinterpret_cast<uintptr_t>(w[r]) & 15) == 0;
+  if (wide) {
+    const int chunks = n >> 3;
+    auto use = [&](uint4 raw, int chunk, float& acc) {
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float4 a0 = *reinterpret_cast<const float4*>(a + 8 * chunk), a1 = *reinterpret_cast<const float4*>(a + 8 * chunk + 4);
+      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+      const float2 f2 = __bfloat1622float2(p2[2]), f3 = __bfloat1622float2(p2[3]);
+      acc = fmaf(f0.x, a0.x, acc); acc = fmaf(f0.y, a0.y, acc); acc = fmaf(f1.x, a0.z, acc); acc = fmaf(f1.y, a0.w, acc);
+      acc = fmaf(f2.x, a1.x, acc); acc = fmaf(f2.y, a1.y, acc); acc = fmaf(f3.x, a1.z, acc); acc = fmaf(f3.y, a1.w, acc);
+    };
+    int i = lane;
+    for (; i + 32 < chunks; i += 64) {
+      uint4 lo[NR], hi[NR];
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        lo[r] = __ldg(reinterpret_cast<const uint4*>(w[r]) + i);
+        hi[r] = __ldg(reinterpret_cast<const uint4*>(w[r]) + i + 32);
+      }
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        use(lo[r], i, s[r]);
+        use(hi[r], i + 32, s[r]);
+      }
+    }
+    for (; i < chunks; i += 32) {
+      uint4 lo[NR];
+#pragma unroll
+      for (int r = 0; r < NR; ++r) lo[r] = __ldg(reinterpret_cast<const uint4*>(w[r]) + i);
+#pragma unroll
+      for (int r = 0; r < NR; ++r) use(lo[r], i, s[r]);
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) s[r] = fmaf(__bfloat162float(w[r][i]), a[i], s[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NR; ++r) out[r] = warp_sum(s[r]);
+}
+
+template <int NR>
+__device__ __forceinline__ void dot_lanes_rows(const float* const (&w)[NR], const float* __restrict__ a, int n, int lane,
+                                               float (&out)[NR]) {
+#pragma unroll
+  for (int r = 0; r < NR; ++r) out[r] = dot_lanes<float>(w[r], a, n, lane);
+}
+
 constexpr int kMoeWarps = 8;
 
 template <typename T>
@@ -122,9 +181,20 @@ __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_u
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.y * rows_per_block;
   const T* w = w_up + (size_t)e * ff * width;
-  for (int f = f0 + warp; f < min(ff, f0 + rows_per_block); f += kMoeWarps) {
-    const float zf = fmaxf(dot_lanes<T>(w + (size_t)f * width, h_s, width, lane), 0.0f);
-    if (lane == 0) act[(size_t)p * ff + f] = from_f32<T>(zf * zf);
+  const int last = min(ff, f0 + rows_per_block) - 1;
+  for (int f = f0 + warp; f <= last; f += 4 * kMoeWarps) {           // four rows of a warp at a time
+    const T* rows[4];
+    float z[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) rows[r] = w + (size_t)min(f + r * kMoeWarps, last) * width;
+    dot_lanes_rows<4>(rows, h_s, width, lane, z);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float zf = fmaxf(z[r], 0.0f);
+        if (f + r * kMoeWarps <= last) act[(size_t)p * ff + f + r * kMoeWarps] = from_f32<T>(zf * zf);
+      }
+    }
   }
 }
 
@@ -158,12 +228,16 @@ __global__ void moe_down_kernel(const T* __restrict__ h, const T* __restrict__ a
     __syncthreads();
     const T* w = w_down + (size_t)e * width * ff;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const int row = c0 + warp + kMoeWarps * r;
-      if (row < c1) {
-        const float d = dot_lanes<T>(w + (size_t)row * ff, a_s, ff, lane);
-        acc[r] = fmaf(g, d, acc[r]);
-      }
+    for (int r0 = 0; r0 < 8; r0 += 4) {
+      if (c0 + warp + kMoeWarps * r0 >= c1) break;
+      const T* rows[4];
+      float d[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) rows[r] = w + (size_t)min(c0 + warp + kMoeWarps * (r0 + r), c1 - 1) * ff;
+      dot_lanes_rows<4>(rows, a_s, ff, lane, d);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        if (c0 + warp + kMoeWarps * (r0 + r) < c1) acc[r0 + r] = fmaf(g, d[r], acc[r0 + r]);
     }
   }
   if (lane == 0) {
@@ -265,7 +339,7 @@ int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const i
   if (T <= 0) return 0;
   if (top <= 0 || experts < 0 || width <= 0 || ff <= 0) return IFX_E_BADARG;
   if ((size_t)width * 4 > 160 * 1024 || (size_t)ff * 4 > 160 * 1024) return IFX_E_TOOBIG;
-  const int up_rows = 32, down_rows = T <= 64 ? 16 : 64;  // few tokens: more blocks, so that more bytes are in flight
+  const int up_rows = 32, down_rows = T <= 64 ? 32 : 64;  // few tokens: more blocks, so that more bytes are in flight
   dim3 grid_up(T * top, (ff + up_rows - 1) / up_rows), grid_down(T, (width + down_rows - 1) / down_rows);
   const size_t smem_up = (size_t)width * 4, smem_down = (size_t)ff * 4;
 #define IFX_MOE(TT, TO)                                                                                           \

@@ -1037,13 +1037,17 @@ class CudaKernels:
         return out
 
     def wkv_scan(self, r, k, v, w_raw, g, w0, u, norm_w, eps, heads, dim, state, prev_offset, x, ctx, out_dtype):
-        """The recurrence of csrc/wkv.cu over every request's tokens.  r, k, v, w_raw, g: float32 [T, heads * dim];
+        """The recurrence of csrc/wkv.cu over every request's tokens.  r, k, v, w_raw, g: float32 [T, heads * dim], each
+        contiguous or a column block of a wider matrix (all with the same distance between rows);
         `state`: float32 [slots, heads * dim * dim + C], the matrices first, then the last input row, both moved on.
         Returns out / rms(out) per head * norm_w * silu(g) in `out_dtype`."""
         T, HD = r.shape
         C = x.shape[1]
+        ld, ld_w = max(int(r.stride(0)), HD), max(int(w_raw.stride(0)), HD)
         for t in (r, k, v, w_raw, g):
-            _need(t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (T, HD), "wkv_scan: float32 [T, heads * dim] inputs")
+            _need(t.dtype == torch.float32 and tuple(t.shape) == (T, HD) and t.stride(1) == 1
+                  and (T == 1 or t.stride(0) == (ld_w if t is w_raw else ld)),
+                  "wkv_scan: float32 [T, heads * dim] inputs; r, k, v and g with one distance between rows")
         for t in (w0, u, norm_w):
             _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == HD, "wkv_scan: float32 constants of heads * dim")
         _need(HD == heads * dim and prev_offset == heads * dim * dim and state.dtype == torch.float32 and state.is_contiguous()
@@ -1054,7 +1058,7 @@ class CudaKernels:
         _check(self.lib.ifx_wkv_scan(
             _ptr(r), _ptr(k), _ptr(v), _ptr(w_raw), _ptr(g), _ptr(w0), _ptr(u), _ptr(norm_w), ctypes.c_float(eps),
             _ptr(state), ctypes.c_void_p(state.data_ptr() + 4 * prev_offset), ctypes.c_longlong(state.shape[1]), _ptr(x), C,
-            _ptr(ctx.cu_seqlens), _ptr(ctx.req_slot), _ptr(scratch), _ptr(y), ctx.num_requests, T, heads, dim, _DT[out_dtype],
+            _ptr(ctx.cu_seqlens), _ptr(ctx.req_slot), _ptr(scratch), _ptr(y), ctx.num_requests, T, heads, dim, ld, ld_w, _DT[out_dtype],
             _stream()), "wkv_scan")
         self.launches += 1
         return y

@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(kScanThreads) wkv_scan_kernel(
     const float* __restrict__ u, const float* __restrict__ norm_w, float eps, float* __restrict__ s_state,
     float* __restrict__ prev_state, long long slot_stride, const float* __restrict__ x, int C,
     const int* __restrict__ cu_seqlens, const int* __restrict__ req_slot, float* __restrict__ o_scratch,
-    TO* __restrict__ y, int H, int D, int DC, int TB, int fused_norm, int wide_copies) {
+    TO* __restrict__ y, int H, int D, int DC, int TB, int fused_norm, int wide_copies, int ld, int ld_w) {
   extern __shared__ __align__(16) float smem[];
   constexpr int DP = KS * R;                         // a staged row of r, k or w: D numbers, then zeros up to KS * R
   const int per_buf = TB * (3 * DP + DC);
@@ -126,26 +126,26 @@ __global__ void __launch_bounds__(kScanThreads) wkv_scan_kernel(
       const int d4 = D >> 2, c4 = cols >> 2;
       for (int idx = tid; idx < nt * d4; idx += blockDim.x) {
         const int tt = idx / d4, i = (idx % d4) * 4;
-        const size_t src = (size_t)(t0 + tt) * HD + (size_t)head * D + i;
+        const size_t src = (size_t)(t0 + tt) * ld + (size_t)head * D + i;
         cp_async_16(r_s + tt * DP + i, r + src);
         cp_async_16(k_s + tt * DP + i, k + src);
-        cp_async_16(w_s + tt * DP + i, w_raw + src);
+        cp_async_16(w_s + tt * DP + i, w_raw + (size_t)(t0 + tt) * ld_w + (size_t)head * D + i);
       }
       for (int idx = tid; idx < nt * c4; idx += blockDim.x) {
         const int tt = idx / c4, i = (idx % c4) * 4;
-        cp_async_16(v_s + tt * DC + i, v + (size_t)(t0 + tt) * HD + (size_t)head * D + j0 + i);
+        cp_async_16(v_s + tt * DC + i, v + (size_t)(t0 + tt) * ld + (size_t)head * D + j0 + i);
       }
     } else {
       for (int idx = tid; idx < nt * D; idx += blockDim.x) {
         const int tt = idx / D, i = idx % D;
-        const size_t src = (size_t)(t0 + tt) * HD + (size_t)head * D + i;
+        const size_t src = (size_t)(t0 + tt) * ld + (size_t)head * D + i;
         cp_async_4(r_s + tt * DP + i, r + src);
         cp_async_4(k_s + tt * DP + i, k + src);
-        cp_async_4(w_s + tt * DP + i, w_raw + src);
+        cp_async_4(w_s + tt * DP + i, w_raw + (size_t)(t0 + tt) * ld_w + (size_t)head * D + i);
       }
       for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
         const int tt = idx / cols, i = idx % cols;
-        cp_async_4(v_s + tt * DC + i, v + (size_t)(t0 + tt) * HD + (size_t)head * D + j0 + i);
+        cp_async_4(v_s + tt * DC + i, v + (size_t)(t0 + tt) * ld + (size_t)head * D + j0 + i);
       }
     }
   };
@@ -206,18 +206,19 @@ __global__ void __launch_bounds__(kScanThreads) wkv_scan_kernel(
   // the block's own writes to o_scratch are visible to it after the barrier at the end of the loop
   for (int t = lo + warp; t < hi; t += nwarps) {
     const size_t base = (size_t)t * HD + (size_t)head * D;
-    wkv_head_norm<TO>(o_scratch + base, g + base, norm_w + head * D, eps, y + base, D, lane);
+    wkv_head_norm<TO>(o_scratch + base, g + (size_t)t * ld + (size_t)head * D, norm_w + head * D, eps, y + base, D, lane);
   }
 }
 
 template <typename TO>
 __global__ void wkv_norm_kernel(const float* __restrict__ o, const float* __restrict__ g, const float* __restrict__ norm_w,
-                                float eps, TO* __restrict__ y, long long items, int H, int D) {
+                                float eps, TO* __restrict__ y, long long items, int H, int D, int ld) {
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= items) return;
   const int head = (int)(item % H);
   const size_t base = (size_t)item * D;              // item = token * H + head
-  wkv_head_norm<TO>(o + base, g + base, norm_w + head * D, eps, y + base, D, threadIdx.x & 31);
+  wkv_head_norm<TO>(o + base, g + (size_t)(item / H) * ld + (size_t)head * D, norm_w + head * D, eps, y + base, D,
+                    threadIdx.x & 31);
 }
 
 }  // namespace ifx
@@ -231,7 +232,7 @@ int ifx_token_shift_mix(const float* x, const float* mu, const float* prev_state
                         int n_mix, int out_dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (C <= 0 || n_mix <= 0 || prev_state == nullptr) return IFX_E_BADARG;
-  const int threads = C >= 1024 ? 256 : (C >= 256 ? 128 : 64);
+  const int threads = T <= 64 ? (C >= 2048 ? 1024 : (C >= 512 ? 512 : 128)) : (C >= 1024 ? 256 : (C >= 256 ? 128 : 64));
   if (out_dtype == IFX_DT_F32)
     token_shift_mix_kernel<float><<<T, threads, 0, stream>>>(x, mu, prev_state, slot_stride, token_req, req_slot,
                                                               cu_seqlens, (float*)out, T, C, n_mix);
@@ -267,15 +268,16 @@ int ifx_tanh_rows(void* z, long long n, int dtype, cudaStream_t stream) {
   return 0;
 }
 
-// r, k, v, w_raw, g: float32 [T, H * D].  s_state / prev_state: slot 0's matrix block [H, D, D] and input row [C]
+// r, k, v, w_raw, g: float32 [T, H * D] in rows `ld` floats apart (`ld_w` for w_raw): they may be column
+// blocks of one wider matrix.  s_state / prev_state: slot 0's matrix block [H, D, D] and input row [C]
 // inside the state tensor, slots slot_stride floats apart.  o_scratch: float32 [T, H * D].  y: [T, H * D].
 int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_raw, const float* g, const float* w0,
                  const float* u, const float* norm_w, float eps, float* s_state, float* prev_state,
                  long long slot_stride, const float* x, int C, const int* cu_seqlens, const int* req_slot,
-                 float* o_scratch, void* y, int num_requests, int num_tokens, int H, int D, int out_dtype,
+                 float* o_scratch, void* y, int num_requests, int num_tokens, int H, int D, int ld, int ld_w, int out_dtype,
                  cudaStream_t stream) {
   if (num_requests <= 0 || num_tokens <= 0) return 0;
-  if (H <= 0 || D <= 0 || D > 256 || H > 65535) return IFX_E_BADARG;
+  if (H <= 0 || D <= 0 || D > 256 || H > 65535 || ld < H * D || ld_w < H * D) return IFX_E_BADARG;
   // threads per value channel (a power of two that depends on the head size alone, so that a sum's order does too)
   // and key channels per thread: four, eight for the largest heads
   int ks = 1;
@@ -292,7 +294,7 @@ int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_
   int tb = longest < 32 ? (longest < 16 ? 16 : longest) : 32;
   while (tb > 4 && ((size_t)2 * tb * (3 * dp + dc) + tb) * sizeof(float) > 160 * 1024) tb /= 2;
   const size_t smem = ((size_t)2 * tb * (3 * dp + dc) + tb) * sizeof(float);
-  const int wide = (D % 4 == 0 && dc % 4 == 0 && ((uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)w_raw) % 16 == 0) ? 1 : 0;
+  const int wide = (D % 4 == 0 && dc % 4 == 0 && ld % 4 == 0 && ld_w % 4 == 0 && ((uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)w_raw) % 16 == 0) ? 1 : 0;
   const int fused = groups == 1 ? 1 : 0;
   dim3 grid(num_requests, H, groups);
 #define IFX_SCAN(KS_, R_, TO)                                                                                    \
@@ -300,10 +302,10 @@ int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_
     auto kern = wkv_scan_kernel<KS_, R_, TO>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     kern<<<grid, threads, smem, stream>>>(r, k, v, w_raw, g, w0, u, norm_w, eps, s_state, prev_state, slot_stride, \
-                                          x, C, cu_seqlens, req_slot, o_scratch, (TO*)y, H, D, dc, tb, fused, wide); \
+                                          x, C, cu_seqlens, req_slot, o_scratch, (TO*)y, H, D, dc, tb, fused, wide, ld, ld_w); \
     if (!fused) {                                                                                                \
       const long long items = (long long)num_tokens * H;                                                        \
-      wkv_norm_kernel<TO><<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(o_scratch, g, norm_w, eps, (TO*)y, items, H, D); \
+      wkv_norm_kernel<TO><<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(o_scratch, g, norm_w, eps, (TO*)y, items, H, D, ld); \
     }                                                                                                            \
   } while (0)
 #define IFX_SCAN_KS(TO)                                   \

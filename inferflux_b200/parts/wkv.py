@@ -31,6 +31,7 @@ class WKV(Mixer):
     names (tensor names of mu_r .. mu_w, r, k, v, g, w1, w2, w0, u, norm, o)."""
 
     takes_stream = True               # the mixes are made from the float32 rows
+    STACK_MAX_TOKENS = 32             # up to this many tokens a step the four projections run as one product
 
     _NAMES = {"mu_r": "mu.r", "mu_k": "mu.k", "mu_v": "mu.v", "mu_g": "mu.g", "mu_w": "mu.w", "r": "r", "k": "k",
               "v": "v", "g": "g", "w1": "w1", "w2": "w2", "w0": "w0", "u": "u", "norm": "norm", "o": "o"}
@@ -76,19 +77,23 @@ class WKV(Mixer):
         rank = int(tensors[n["w1"]].shape[0])
         if tensors[n["w2"]].shape[1] != rank:
             raise ValueError(f"wkv: the decay's two matrices meet at {rank} and {tensors[n['w2']].shape[1]}")
-        layout = {s: ((HD, C), dtype) for s in ("r", "k", "v", "g")}
+        layout = {"rkvg": ((4 * HD, C), dtype)}             # the four projections one below the other
         layout.update({"w1": ((rank, C), dtype), "w2": ((HD, rank), dtype), "o": ((C, HD), dtype),
                        "mu": ((len(_MIXES), C), torch.float32), "w0": ((HD,), torch.float32),
                        "u": ((HD,), torch.float32), "norm": ((HD,), torch.float32)})
         self.buffers = buf = WeightBuffers(device, layout)
-        for s in ("r", "k", "v", "g", "w1", "w2", "o"):
+        for i, s in enumerate(("r", "k", "v", "g")):
+            buf["rkvg"][i * HD:(i + 1) * HD].copy_(tensors[n[s]])
+        for s in ("w1", "w2", "o"):
             buf[s].copy_(tensors[n[s]])
         for i, s in enumerate(_MIXES):
             buf["mu"][i].copy_(tensors[n["mu_" + s]])
         buf["w0"].copy_(tensors[n["w0"]])
         buf["u"].copy_(tensors[n["u"]].reshape(HD))
         buf["norm"].copy_(tensors[n["norm"]])
-        self.w = {s: buf[s] for s in ("r", "k", "v", "g", "w1", "w2", "o")}
+        self.w = {s: buf[s] for s in ("w1", "w2", "o")}
+        self.w.update({s: buf["rkvg"][i * HD:(i + 1) * HD] for i, s in enumerate(("r", "k", "v", "g"))})
+        self.w_rkvg = buf["rkvg"]
         self.mu, self.w0, self.u, self.norm_w = buf["mu"], buf["w0"], buf["u"], buf["norm"]
         self.rank = rank
 
@@ -99,7 +104,14 @@ class WKV(Mixer):
         f32 = torch.float32
         matrices = self.heads * self.dim * self.dim
         mixes = k.token_shift_mix(x, self.mu, cache.state, matrices, ctx, ctx.dtype)          # [5, T, hidden]
-        r, kk, v, g = (k.linear(mixes[i], self.w[s], out_dtype=f32) for i, s in enumerate(("r", "k", "v", "g")))
+        T, HD = x.shape[0], self.heads * self.dim
+        if ctx.dtype == torch.bfloat16 and T <= self.STACK_MAX_TOKENS:
+            # few tokens: a step reads every weight once whatever it computes, so the four mixes go through the four
+            # stacked matrices in one product (of its sixteen blocks the four on the diagonal are used)
+            both = k.materialize(k.linear(mixes[:4].view(4 * T, self.hidden), self.w_rkvg, out_dtype=f32, allow_partial=True))
+            r, kk, v, g = (both[i * T:(i + 1) * T, i * HD:(i + 1) * HD] for i in range(4))
+        else:
+            r, kk, v, g = (k.linear(mixes[i], self.w[s], out_dtype=f32) for i, s in enumerate(("r", "k", "v", "g")))
         low = k.tanh(k.linear(mixes[4], self.w["w1"]))                                         # [T, rank]
         w_raw = k.linear(low, self.w["w2"], out_dtype=f32)
         y = k.wkv_scan(r, kk, v, w_raw, g, self.w0, self.u, self.norm_w, self.eps, self.heads, self.dim,
