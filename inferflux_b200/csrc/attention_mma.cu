@@ -35,20 +35,6 @@
 
 namespace ifx {
 
-// Which keys a query sees besides "not later than itself": the last `window` of them (> 0), only those of its own
-// stretch of `chunk` positions (> 0), or both; `sink`: the softmax's denominator holds one more unit, a key of score 0
-// that brings no value.
-struct KeyMask {
-  int window, chunk, sink;
-  __device__ __forceinline__ int first(int pos) const {          // the first key the query at `pos` sees
-    int f = window > 0 ? max(0, pos - window + 1) : 0;
-    if (chunk > 0) f = max(f, pos / chunk * chunk);
-    return f;
-  }
-  __device__ __forceinline__ bool any() const { return window > 0 || chunk > 0; }
-};
-
-
 namespace cg = cooperative_groups;
 typedef __nv_bfloat16 bf16;
 

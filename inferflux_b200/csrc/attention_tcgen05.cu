@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kThreads)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap pool_map,
                             const int* __restrict__ block_table, const int* __restrict__ tiles,
                             const int* __restrict__ req_slot, bf16* __restrict__ out, int nq, int nkv, int page_size,
-                            int page_shift, int max_blocks, int num_pages, int window, float scale_log2,
+                            int page_shift, int max_blocks, int num_pages, KeyMask window, float scale_log2,
                             int* __restrict__ error_flag) {
   using L = PrefillLayout<D>;
   constexpr int HALVES = L::HALVES, SLOTS = L::SLOTS;
@@ -174,12 +174,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const int g = h / (nq / nkv);
   // key tiles [tb_q, te_q) of query tile q (rows q * 128 ...); tile 1 may be absent
   const int rows_1 = max(rows - kBM, 0);
-  const int tb_0 = (window > 0 ? max(0, pos0 - window + 1) : 0) / kBN;
+  const int tb_0 = window.first(pos0) / kBN;
   const int te_0 = (pos0 + min(rows, kBM) + kBN - 1) / kBN;
-  const int tb_1 = (window > 0 ? max(0, pos0 + kBM - window + 1) : 0) / kBN;
+  const int tb_1 = window.first(pos0 + kBM) / kBN;
   const int te_1 = rows_1 > 0 ? (pos0 + rows + kBN - 1) / kBN : tb_1;
   const int tb = tb_0, te = max(te_0, te_1);
-  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0, kend = pos0 + rows;
+  const int kfirst = window.first(pos0), kend = pos0 + rows;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ fetching
@@ -288,7 +288,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int rows_q = q == 0 ? min(rows, kBM) : rows_1;
     const int pos0_q = pos0 + q * kBM;
     const int pos = pos0_q + row;
-    const int wfirst = window > 0 ? pos - window + 1 : 0;
+    const int wfirst = window.first(pos);
     const int tb_q = q == 0 ? tb_0 : tb_1, te_q = q == 0 ? te_0 : te_1;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_addr = tmem_s + q * kBN + lane_addr, o_addr = tmem_o + q * D + lane_addr;
@@ -300,7 +300,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_S_FULL + q), i & 1));
       if (!ok) break;
       tc_fence_after();
-      const bool edge = key0 + kBN - 1 > pos0_q || (window > 0 && key0 < pos0_q + kBM - window);
+      const bool edge = key0 + kBN - 1 > pos0_q || (window.any() && key0 < window.first(pos0_q + kBM - 1));
       // pass 1: the row's maximum
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -383,6 +383,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     if (!ok && lane == 0) atomicExch(error_flag, 9);
     if (ok && i > 0) {
       tc_fence_after();
+      if (window.sink && m_ref > -INFINITY) l_run += exp2f(-m_ref * scale_log2);     // the sink's share
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       bf16* dst = out + ((size_t)(row0 + q * kBM + row) * nq + h) * D;
 #pragma unroll 1
@@ -414,7 +415,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 template <int D>
 static int launch_prefill_tcgen05(const bf16* q, int num_tokens, const bf16* kv_pool, const int* block_table,
                                   const int* tiles, const int* req_slot, bf16* out, int num_tiles, int nq, int nkv,
-                                  int page_size, int page_shift, int max_blocks, int num_pages, int window,
+                                  int page_size, int page_shift, int max_blocks, int num_pages, KeyMask window,
                                   float scale_log2, int* error_flag, cudaStream_t stream) {
   CUtensorMap q_map, pool_map;
   int rc = make_tensor_map_bf16(&q_map, q, num_tokens, nq * D, kBM);
@@ -447,10 +448,12 @@ int ifx_attention_prefill_tcgen05_supports(int d, int page_size) {
 
 // q [num_tokens, nq * d] bfloat16, 16-byte aligned.  tiles: int32 [num_tiles, 4] = (request index, first
 // flat row, rows <= 256, first position).
-int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
-                                  const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
-                                  int d, int page_size, int max_blocks, int num_pages, int window, float scale,
-                                  int* error_flag, cudaStream_t stream) {
+// chunk, sink: see KeyMask (common.cuh).
+int ifx_attention_prefill_tcgen05_ex(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
+                                     const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
+                                     int d, int page_size, int max_blocks, int num_pages, int window_size, int chunk,
+                                     int sink, float scale, int* error_flag, cudaStream_t stream) {
+  const KeyMask window{window_size, chunk, sink};
   if (num_tiles <= 0) return 0;
   if (!ifx_attention_prefill_tcgen05_supports(d, page_size) || nq <= 0 || nkv <= 0 || nq % nkv || max_blocks <= 0 ||
       num_tiles > 65535 || !(scale > 0.0f) || error_flag == nullptr)
@@ -465,6 +468,14 @@ int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_
   return launch_prefill_tcgen05<128>((const bf16*)q, num_tokens, (const bf16*)kv_pool, block_table, tiles, req_slot,
                                      (bf16*)out, num_tiles, nq, nkv, page_size, ps, max_blocks, num_pages, window,
                                      scale_log2, error_flag, stream);
+}
+
+int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
+                                  const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
+                                  int d, int page_size, int max_blocks, int num_pages, int window, float scale,
+                                  int* error_flag, cudaStream_t stream) {
+  return ifx_attention_prefill_tcgen05_ex(q, num_tokens, kv_pool, block_table, tiles, req_slot, out, num_tiles, nq, nkv, d,
+                                          page_size, max_blocks, num_pages, window, 0, 0, scale, error_flag, stream);
 }
 
 }  // extern "C"

@@ -147,7 +147,7 @@ class CudaKernels:
                    "ifx_attention_generic_ex", "ifx_norm_rope_append", "ifx_token_shift_mix", "ifx_cast_rows",
                    "ifx_wkv_scan", "ifx_moe_route", "ifx_moe_experts", "ifx_tanh_rows",
                    "ifx_attention_prefill_bf16_ex", "ifx_attention_decode_bf16_ex", "ifx_moe_sorted_rows", "ifx_moe_sort",
-                   "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped"):
+                   "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped", "ifx_attention_prefill_tcgen05_ex"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
@@ -781,7 +781,13 @@ class CudaKernels:
                     ctx.extra_len[name] = len(vals)
             num_tiles = ctx.extra_len["attn.prefill_tiles"] // 4
             common = (cache.page_size, table.shape[1], kv.shape[0], win, int(chunk or 0), int(bool(sink)), ctypes.c_float(scale))
-            if num_tiles:
+            if num_tiles and self.tensor_core_prefill and self.lib.ifx_attention_prefill_tcgen05_supports(d, cache.page_size):
+                _check(self.lib.ifx_attention_prefill_tcgen05_ex(
+                    _ptr(q), T, _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.prefill_tiles"]), _ptr(ctx.req_slot), _ptr(out),
+                    num_tiles, nq, nkv, d, *common, _ptr(self.error_flag), _stream()),
+                    "attention (masked, prompt portions, tcgen05)")
+                self.launches += 1
+            elif num_tiles:
                 _check(self.lib.ifx_attention_prefill_bf16_ex(
                     _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.prefill_tiles"]), _ptr(ctx.req_slot), _ptr(out),
                     num_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),

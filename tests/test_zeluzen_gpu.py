@@ -302,7 +302,8 @@ def test_attention_with_chunks_and_sink_planted_keys(cuda_kernels, dtype, tol, c
 @pytest.mark.parametrize("sizes", [(8, 2, 128, 16), (4, 4, 64, 16), (6, 2, 32, 8), (16, 1, 96, 32)])
 def test_masked_attention_tiles_against_the_per_token_kernel(cuda_kernels, chunk, sizes, monkeypatch):
     """bfloat16: three requests with 1,500, 700 and 40 cached keys; a step that decodes one token of the first two and
-    brings a portion of 300 of a fourth, and a step of single tokens only (the key range cut over a cluster)."""
+    brings a portion of 300 of a fourth, a step with that request's next 333 tokens (tiles that begin in the middle of
+    a chunk), and a step of single tokens only (the key range cut over a cluster)."""
     from inferflux_b200.cache import CacheManager
     from inferflux_b200.config import ScheduleEntry
     from inferflux_b200.engine.batch import StepContext, StepEntry
@@ -332,7 +333,7 @@ def test_masked_attention_tiles_against_the_per_token_kernel(cuda_kernels, chunk
         return ctx
     step([("a", 1499), ("b", 699), ("c", 39)])
     view = cache.view(ScheduleEntry(0, 0))
-    for spans in ([("a", 1), ("b", 1), ("d", 300)], [("a", 1), ("b", 1), ("c", 1)]):
+    for spans in ([("a", 1), ("b", 1), ("d", 300)], [("d", 333), ("c", 1)], [("a", 1), ("b", 1), ("c", 1)]):
         ctx = step(spans)
         T = ctx.num_tokens
         q = _rnd(T, nq * d, seed=T).to(bf).to(DEV)
