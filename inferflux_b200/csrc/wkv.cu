@@ -282,7 +282,18 @@ int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_
   // and key channels per thread: four, eight for the largest heads
   int ks = 1;
   while (ks < 32 && ks * 4 < D) ks *= 2;
-  const int rows = ks * 4 >= D ? 4 : 8;
+  int rows = ks * 4 >= D ? 4 : 8;
+  const int longest = num_tokens - (num_requests - 1);                 // no span is longer than this
+  // A bfloat16 run's long spans (prompt portions) are bound by the latency of one warp's instructions per token:
+  // two key channels a thread make twice the warps with half the work each.  The float32 run keeps one split per
+  // head size, so that its sums have one order however the tokens are cut.
+  // (measured on one prompt of 2,048 tokens: 24 heads of 64 channels 631 -> 530 us, but 56 heads 631 -> 727 us: with
+  // enough threads to fill the SMs the extra shuffles only cost)
+  if (out_dtype == IFX_DT_BF16 && longest >= 64 && rows == 4 && ks <= 16 && ks * 4 == D && D >= 16 &&
+      (long long)num_requests * H * D * ks < 40000) {
+    ks *= 2;
+    rows = 2;
+  }
   const int dp = ks * rows;
   // value channels per block: as many as a block holds; fewer while the grid does not fill the SMs
   int dc = D;
@@ -290,8 +301,7 @@ int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_
   while ((long long)num_requests * H * ((D + dc - 1) / dc) < 148 && dc * ks > 64 && dc % 8 == 0) dc /= 2;
   const int groups = (D + dc - 1) / dc;
   const int threads = (dc * ks + 31) / 32 * 32;
-  const int longest = num_tokens - (num_requests - 1);                 // no span is longer than this
-  int tb = longest < 32 ? (longest < 16 ? 16 : longest) : 32;
+  int tb = longest < 32 ? (longest < 16 ? 16 : longest) : (longest >= 128 ? 64 : 32);
   while (tb > 4 && ((size_t)2 * tb * (3 * dp + dc) + tb) * sizeof(float) > 160 * 1024) tb /= 2;
   const size_t smem = ((size_t)2 * tb * (3 * dp + dc) + tb) * sizeof(float);
   const int wide = (D % 4 == 0 && dc % 4 == 0 && ld % 4 == 0 && ld_w % 4 == 0 && ((uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)w_raw) % 16 == 0) ? 1 : 0;
@@ -310,7 +320,10 @@ int ifx_wkv_scan(const float* r, const float* k, const float* v, const float* w_
   } while (0)
 #define IFX_SCAN_KS(TO)                                   \
   do {                                                    \
-    if (rows == 8) IFX_SCAN(32, 8, TO);                   \
+    if (rows == 2 && ks == 8) IFX_SCAN(8, 2, TO);         \
+    else if (rows == 2 && ks == 16) IFX_SCAN(16, 2, TO);  \
+    else if (rows == 2) IFX_SCAN(32, 2, TO);              \
+    else if (rows == 8) IFX_SCAN(32, 8, TO);              \
     else if (ks == 1) IFX_SCAN(1, 4, TO);                 \
     else if (ks == 2) IFX_SCAN(2, 4, TO);                 \
     else if (ks == 4) IFX_SCAN(4, 4, TO);                 \
