@@ -440,6 +440,62 @@ def test_float32_is_the_same_under_every_cutting(name, zeluzen_dirs, oracle, cud
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_medium_model_with_long_prompts(dtype, tmp_path, cuda_kernels):
+    """Prompts of 700 and 300 tokens through a model of seven layers: whole, then in portions of 128 and 200 beside
+    each other's decoded tokens.  These steps reach the kernels of many rows (library and tcgen05 products, sorted
+    expert tiles, the tensor-core attention with chunks and a sink, the scan's long spans) inside a whole model."""
+    from inferflux_b200.engine import StepEntry
+    raw, page = zm.medium_config()
+    d = zm.write_model(raw, tmp_path / "medium", seed=77)
+    reqs = zm.requests_for(raw, [700, 300], 12)
+    rows = {"r0": [0, 1, 127, 128, 129, 255, 256, 257, 383, 384, 511, 512, 640, 698, 699], "r1": [0, 63, 64, 127, 128, 200, 298, 299]}
+    rounded = torch.bfloat16 if dtype == "bfloat16" else None
+    want = {k: v[rows[k]] for k, v in zm.plain_logits(d, reqs, weights_as=rounded).items()}
+    yard = {k: v[rows[k]] for k, v in zm.plain_logits(d, reqs, weights_as=torch.bfloat16, dtype=torch.bfloat16).items()} \
+        if dtype == "bfloat16" else None
+
+    def compare(name, got):
+        for rid in reqs:
+            if dtype == "float32":
+                assert float(np.abs(got[rid] - want[rid]).max()) < 5e-4, (name, rid, float(np.abs(got[rid] - want[rid]).max()))
+            else:
+                _bf16_close(f"{name} {rid}", got[rid], want[rid], yard[rid])
+    from inferflux_b200.engine import ModelRunner
+    from inferflux_b200.models import load_model
+    _c, model = load_model(d, dtype=dtype, device=DEV)
+    runner = ModelRunner(model, cuda_kernels, page_size=page, num_pages=80, max_seqs=4, max_seq_len=1024)
+    got = {}
+    for rid, toks in reqs.items():
+        got[rid] = runner.step([StepEntry(rid, toks, rows[rid])]).cpu().numpy()
+        runner.end_request(rid)
+    cuda_kernels.check_errors()
+    compare("whole", got)
+    # portions of both side by side, then the last tokens one by one beside the other's portions
+    got = {rid: {} for rid in reqs}
+    at = {"r0": 0, "r1": 0}
+    size = {"r0": 200, "r1": 128}
+    while any(at[r] < len(reqs[r]) for r in reqs):
+        entries, asked = [], []
+        for rid, toks in reqs.items():
+            if at[rid] >= len(toks):
+                continue
+            n = 1 if len(toks) - at[rid] <= 20 else min(size[rid], len(toks) - 20 - at[rid])
+            w = [p - at[rid] for p in rows[rid] if at[rid] <= p < at[rid] + n]
+            entries.append(StepEntry(rid, toks[at[rid]:at[rid] + n], w))
+            asked += [(rid, p) for p in rows[rid] if at[rid] <= p < at[rid] + n]
+            at[rid] += n
+        out = runner.step(entries).cpu().numpy()
+        for (rid, p), row in zip(asked, out):
+            got[rid][p] = row
+        for rid in reqs:
+            if at[rid] == len(reqs[rid]) and rid in runner.cache:
+                runner.end_request(rid)
+        runner.cache.check()
+    cuda_kernels.check_errors()
+    compare("portions", {rid: np.stack([got[rid][p] for p in rows[rid]]) for rid in reqs})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_with_pages_given_back_and_graphs(dtype, zeluzen_dirs, cuda_kernels):
     """12 prompt tokens, then 300 decoded one by one beside a second request that joins and leaves: chunk borders are
     crossed by decoded tokens, pages are given back and used again, states live in slots, decode steps replay a CUDA graph."""

@@ -69,6 +69,21 @@ def configs():
     return {"A": (a, 8), "B": (b, 16), "C": (c, 4), "D": (d, 16)}
 
 
+def medium_config():
+    """A model of a few hundred columns whose prompts are long enough for the kernels of many rows: heads of 64 and
+    128 on pages of 16 (the tensor-core attention), values as long as keys and longer, chunks of 128 and 256, experts
+    with more than 512 (token, choice) pairs a step, recurrent heads of 32, 64 and 128 channels."""
+    sc = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}
+    return {"architecture": "Zeluzen", "vocab": 700, "width": 320, "norm": {"eps": 1e-6}, "layers": [
+        _attn(8, 2, 64, 64, _dense(448), chunk=128, rot=32, scaling=sc, scale=0.125, base=20000.0),
+        _wkv(5, 64, _moe(96, 8, 2, 3)),
+        _wkv(3, 128, _dense(448), rank=24),
+        _attn(8, 2, 64, 64, _moe(96, 8, 2, 3), chunk=128, rot=32, scaling=sc, scale=0.125, base=20000.0, kv_from=0),
+        _attn(4, 4, 128, 128, None, chunk=256, rot=128, scale=0.09, base=5000.0),
+        _attn(6, 3, 32, 48, _dense(384), chunk=64, rot=16, scale=0.2),
+        _wkv(10, 32, _moe(64, 5, 0, 2))]}, 16
+
+
 def write_model(raw, out_dir, seed):
     """Random weights for `raw`, then made sharp: head norms are large so that attention is peaked (the norms in
     front of the scores take any scale of the projections away), the embedding so that tokens differ, norm weights
