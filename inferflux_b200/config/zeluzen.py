@@ -115,6 +115,8 @@ class ZeluzenConfig:
                     raise ConfigError(f"Zeluzen config: {where}mlp.router chooses {top} of {n} experts (at most 1024)")
 
     def _validate_attention(self, i: int, m: dict, where: str) -> None:
+        m.setdefault("kv_heads", m["heads"])            # left out: a key/value head per query head, values as long as keys
+        m.setdefault("vdim", m["dim"])
         for key in ("kv_heads", "vdim"):
             _integer(where, m, key)
         if m["heads"] % m["kv_heads"]:
